@@ -1,0 +1,317 @@
+/*
+ * rpl_b200.h -- C ABI of librpl.so, the sm_100a (B200) implementation of the
+ * INT8 quantized-inference path of RPL.
+ *
+ * Two layers, both plain C linkage, plain pointers and sizes:
+ *
+ *  1. "rplb_*"  device-level entry points.  Every data pointer is a CUDA device
+ *     pointer on the current device; `stream` is a cudaStream_t passed as
+ *     void* (NULL = the legacy default stream).  Calls are asynchronous on
+ *     that stream unless stated.  Return value: 0 on success, otherwise a
+ *     negative RPLB_E_* code or a positive cudaError_t; rplb_last_error()
+ *     gives the text.
+ *
+ *  2. The reference's own exported names (tensor_quantize_int8, gemm_int8,
+ *     linear_int8 ...), same signatures, struct layouts and ownership rules as
+ *     the reference library, so a program built against the reference's
+ *     include/rpl.h links against this library unchanged.  Each data pointer
+ *     may be a host pointer (staged over PCIe) or a device pointer (used in
+ *     place); results live where the inputs live.  These calls return after
+ *     the result is complete.
+ *
+ * There is no CPU implementation behind any of these: without a CUDA device
+ * every compute entry point fails (rplb_* return an error; the reference-named
+ * producers return NULL and report on stderr, the reference's own convention
+ * for a failed tensor_create, src/rpl_core.c:45).
+ *
+ * If the reference's rpl.h is included first its type definitions are used;
+ * otherwise layout-identical ones are defined here.
+ */
+#ifndef RPL_B200_H
+#define RPL_B200_H
+
+#include <stdint.h>
+#include <stdbool.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------
+ * Types shared with the reference (layouts frozen; x86-64 offsets in
+ * brackets are checked by static assertions in the library).
+ * ---------------------------------------------------------------------- */
+#ifndef RPL_H
+#define RPL_B200_OWN_TYPES 1
+#define MAX_DIMS 8                      /* include/rpl.h:32 */
+
+typedef enum { DEVICE_CPU, DEVICE_GPU } DeviceType;   /* include/rpl.h:23-26 */
+
+/* include/rpl.h:57-78, sizeof 152 */
+typedef struct Tensor {
+    float*    data;                     /* [0]   host or device pointer        */
+    float*    grad;                     /* [8]                                 */
+    uint32_t  dims;                     /* [16]                                */
+    uint32_t  shape[MAX_DIMS];          /* [20]                                */
+    uint32_t  strides[MAX_DIMS];        /* [52]  row-major, in elements        */
+    uint32_t  size;                     /* [84]  product of shape              */
+    bool      requires_grad;            /* [88]                                */
+    void*     _allocation;              /* [96]  what tensor_free releases     */
+    size_t    _alloc_size;              /* [104]                               */
+    DeviceType device;                  /* [112]                               */
+    uint32_t  gpu_buffer;               /* [116]                               */
+    bool      is_leaf;                  /* [120]                               */
+    struct Tensor* parent1;             /* [128]                               */
+    struct Tensor* parent2;             /* [136]                               */
+    void (*backward_fn)(struct Tensor*);/* [144]                               */
+} Tensor;
+
+/* include/rpl.h:167-174, sizeof 56 */
+typedef struct {
+    int8_t*  data;                      /* [0]  separate 64-byte aligned block */
+    float    scale;                     /* [8]                                 */
+    int32_t  zero_point;                /* [12]                                */
+    uint32_t size;                      /* [16]                                */
+    uint32_t dims;                      /* [20]                                */
+    uint32_t shape[MAX_DIMS];           /* [24]                                */
+} QuantizedTensor;
+#endif /* RPL_H */
+
+/* src/rpl_quantization.c:110-118 (private to that file in the reference, but
+ * returned by the exported tensor_quantize_per_channel). */
+typedef struct {
+    int8_t*  data;
+    float*   scales;                    /* one per channel                     */
+    int32_t* zero_points;               /* one per channel, always 0           */
+    uint32_t num_channels;
+    uint32_t channel_size;
+    uint32_t dims;
+    uint32_t shape[8];
+} PerChannelQuantizedTensor;
+
+/* src/rpl_quantization.c:18-24 */
+typedef struct {
+    float    min_val;
+    float    max_val;
+    float    scale;
+    int32_t  zero_point;
+    uint32_t num_samples;
+} QuantizationCalibrator;
+
+/* src/rpl_quantization.c:271-276 */
+typedef struct {
+    Tensor**          fp32_params;
+    QuantizedTensor** int8_params;
+    uint32_t          num_params;
+    bool              is_quantized;
+} QuantizedModel;
+
+/* ------------------------------------------------------------------------
+ * Error codes of the rplb_* layer (CUDA errors are returned as positive
+ * cudaError_t values).
+ * ---------------------------------------------------------------------- */
+#define RPLB_OK              0
+#define RPLB_E_NO_DEVICE    (-1)   /* no CUDA device / driver                  */
+#define RPLB_E_BAD_ARG      (-2)   /* null pointer, misaligned or bad size     */
+#define RPLB_E_TOO_LARGE    (-3)   /* size beyond what the entry point takes   */
+#define RPLB_E_KERNEL       (-4)   /* a kernel reported a bounded wait expired */
+#define RPLB_E_UNSUPPORTED  (-5)   /* shape the selected GEMM kernel can't run */
+
+const char* rplb_last_error(void);          /* text of this thread's last failure */
+int  rplb_device_count(void);               /* 0 when there is no usable device   */
+int  rplb_device_sm_count(void);            /* SMs of the current device           */
+
+/* ------------------------------------------------------------------------
+ * Memory and stream helpers, so that a C host needs no CUDA headers.
+ * ---------------------------------------------------------------------- */
+int  rplb_malloc(void** dptr, size_t bytes);
+int  rplb_free(void* dptr);
+int  rplb_host_alloc(void** hptr, size_t bytes);     /* page-locked host memory */
+int  rplb_host_free(void* hptr);
+int  rplb_copy(void* dst, const void* src, size_t bytes, void* stream);   /* any direction, async */
+int  rplb_stream_sync(void* stream);
+/* 0 = ordinary host memory, 1 = page-locked host, 2 = device, 3 = managed */
+int  rplb_pointer_kind(const void* p);
+
+/* ------------------------------------------------------------------------
+ * Quantization parameters as the reduction kernel leaves them on the device.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    float   min_val;      /* min over non-NaN elements, seeded +FLT_MAX (src/rpl_quantization.c:79-85) */
+    float   max_val;      /* max over non-NaN elements, seeded -FLT_MAX                                */
+    float   scale_sym;    /* fmaxf(|min|,|max|) / 127.0f            (src/rpl_quantization.c:87-88)    */
+    float   scale_asym;   /* (max - min) / 255.0f                   (src/rpl_quantization.c:102-103)  */
+    int32_t zp_asym;      /* (int32) roundf(-min / scale_asym)      (src/rpl_quantization.c:104)      */
+    float   first;        /* x[0]; tensor_get_min_max seeds with it (src/ops_extended.c:54-55)        */
+    float   true_min;     /* min over non-NaN elements, seeded +inf                                    */
+    float   true_max;     /* max over non-NaN elements, seeded -inf                                    */
+} rplb_qparams;           /* 32 bytes */
+
+/* Replaces the min/max loops of tensor_get_min_max (src/ops_extended.c:52-61),
+ * tensor_quantize_int8_symmetric/_asymmetric (src/rpl_quantization.c:79-85,
+ * :96-100) and calibrator_update (src/rpl_quantization.c:33-49).
+ * x: n floats on the device; params: one rplb_qparams on the device.
+ * Uses the library's per-stream scratch buffer (allocated on first use). */
+int  rplb_minmax_f32(const float* x, uint64_t n, rplb_qparams* params, void* stream);
+
+/* Replaces the loop of tensor_quantize_int8 (src/rpl_core.c:521-527):
+ * q = clamp((int32)roundf(x/scale) + zp, -128, 127). */
+int  rplb_quantize_f32_i8(const float* x, int8_t* q, uint64_t n, float scale, int32_t zero_point, void* stream);
+
+/* Same statement with scale (and optionally the zero point) read from device
+ * memory, so that no host round trip separates it from rplb_minmax_f32.
+ * zp_dev may be NULL (zero point 0). */
+int  rplb_quantize_f32_i8_dev(const float* x, int8_t* q, uint64_t n, const float* scale_dev,
+                              const int32_t* zp_dev, void* stream);
+
+/* tensor_quantize_int8_symmetric (src/rpl_quantization.c:77-91) on device
+ * buffers: min/max pass, then quantize with params->scale_sym, zero point 0. */
+int  rplb_quantize_symmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream);
+
+/* tensor_quantize_int8_asymmetric (src/rpl_quantization.c:93-107). */
+int  rplb_quantize_asymmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream);
+
+/* tensor_quantize_per_channel (src/rpl_quantization.c:134-157): channel c is
+ * the contiguous block [c*channel_size, (c+1)*channel_size).  scales and
+ * zero_points (may be NULL) have num_channels entries. */
+int  rplb_quantize_per_channel_f32_i8(const float* x, int8_t* q, float* scales, int32_t* zero_points,
+                                      uint64_t num_channels, uint64_t channel_size, void* stream);
+
+/* tensor_dequantize_int8 (src/ops_extended.c:67-70): out = (float)(q - zp) * scale. */
+int  rplb_dequantize_i8_f32(const int8_t* q, float* out, uint64_t n, float scale, int32_t zero_point, void* stream);
+
+/* Per-channel form of the same statement, out = (float)q * scales[c]; the
+ * reference has no such function (its PerChannelQuantizedTensor has no
+ * dequantizer), the arithmetic is src/ops_extended.c:69 with zp 0. */
+int  rplb_dequantize_per_channel_i8_f32(const int8_t* q, const float* scales, float* out,
+                                        uint64_t num_channels, uint64_t channel_size, void* stream);
+
+/* ------------------------------------------------------------------------
+ * INT8 x INT8 -> INT32 contraction.
+ * ---------------------------------------------------------------------- */
+/* linear_int8 (src/rpl_quantization.c:314-353): out[m,n] = sum_k x[m,k]*w[n,k]
+ * (+ (int8) bias[n] when bias != NULL), raw int32.  x [M,K], w [N,K], out [M,N]. */
+int  rplb_linear_i8_i32(const int8_t* x, const int8_t* w, const int8_t* bias, int32_t* out,
+                        uint64_t M, uint64_t K, uint64_t N, void* stream);
+
+/* gemm_int8 / gemm_int8_fallback, scalar branch (src/ops_extended.c:83-129):
+ * C[i,j] = (int32) roundf( (((float) sum_k (A[i,k]-za)(B[k,j]-zb)) * sa * sb) / sc ),
+ * A [M,K], B [K,N] (row-major), C [M,N]. */
+int  rplb_gemm_i8_requant_i32(const int8_t* A, const int8_t* B, int32_t* C,
+                              uint64_t M, uint64_t N, uint64_t K,
+                              float sa, float sb, float sc, int32_t za, int32_t zb, void* stream);
+
+/* Fused fp32 epilogue (no counterpart function in the reference; it composes
+ * linear_int8 src/rpl_quantization.c:340-350, the dequantize statement
+ * src/ops_extended.c:69, the bias broadcast src/rpl_nn.c:69-71 and ReLU
+ * src/rpl_core.c:254-255):
+ *   out[m,n] = relu?( (((float)acc[m,n] * *a_scale) * w_scales[n]) + bias[n] )
+ * a_scale: one float on the device; w_scales: N floats; bias: N floats or NULL;
+ * ldo: row stride of out in elements (>= N), so a column block of a wider
+ * matrix can be written in place. */
+int  rplb_linear_i8_dequant_f32(const int8_t* x, const int8_t* w, float* out,
+                                uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                                const float* a_scale, const float* w_scales, const float* bias,
+                                int relu, void* stream);
+
+/* tensor_relu_inplace, scalar branch (src/rpl_core.c:254-255): x < 0 -> 0 in
+ * place.  (The fused entry point above applies it inside the GEMM epilogue.) */
+int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
+
+/* Status word of the tensor-core kernel: 0, or the code of the bounded wait
+ * that expired (1 stage-free, 2 stage-loaded, 3 accumulator-free,
+ * 4 accumulator-ready).  Readable at any time; clear != 0 resets it. */
+int  rplb_kernel_status(int clear);
+
+/* Which contraction kernel the three calls above use: 0 = automatic (tcgen05
+ * tensor-core kernel when the shape allows it, else the dp4a kernel),
+ * 1 = dp4a kernel, 2 = tcgen05 kernel (RPLB_E_UNSUPPORTED if the shape does
+ * not fit it).  Returns the previous setting.  Both are CUDA kernels. */
+int  rplb_gemm_backend(int which);
+
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t rplb_launch_count(void);
+
+/* Output-column block of rank `rank` out of `world` when N columns are split
+ * in multiples of `align`: begin and count in columns.  Host arithmetic only. */
+int  rplb_shard_range(uint64_t n, int world, int rank, uint64_t align, uint64_t* begin, uint64_t* count);
+
+/* ------------------------------------------------------------------------
+ * The reference's exported names for the path.  Same signatures, ownership
+ * and struct layouts; data pointers may be host or device pointers.
+ * ---------------------------------------------------------------------- */
+/* include/rpl.h:99-102, src/rpl_core.c:33-77 */
+Tensor* tensor_create(uint32_t dims, const uint32_t* shape, bool requires_grad);
+void    tensor_free(Tensor* t);
+void*   rpitorch_aligned_alloc(size_t alignment, size_t size);
+void    rpitorch_aligned_free(void* ptr);
+
+/* include/rpl.h:176, src/rpl_core.c:511-530 */
+QuantizedTensor* tensor_quantize_int8(const Tensor* input, float scale, int32_t zero_point);
+/* include/rpl.h:177, src/ops_extended.c:75-80 */
+void    quantized_tensor_free(QuantizedTensor* qt);
+/* include/rpl.h:178, src/ops_extended.c:52-61 */
+void    tensor_get_min_max(const Tensor* t, float* min_val, float* max_val);
+/* include/rpl.h:186, src/ops_extended.c:64-73 */
+Tensor* tensor_dequantize_int8(QuantizedTensor* input);
+/* include/rpl.h:187, src/ops_extended.c:124-129 and :83-123 */
+void    gemm_int8(const int8_t* A, const int8_t* B, int32_t* C, uint32_t M, uint32_t N, uint32_t K,
+                  float scale_a, float scale_b, float scale_c, int32_t zero_point_a, int32_t zero_point_b);
+void    gemm_int8_fallback(const int8_t* A, const int8_t* B, int32_t* C, uint32_t M, uint32_t N, uint32_t K,
+                           float scale_a, float scale_b, float scale_c, int32_t zero_point_a, int32_t zero_point_b);
+
+/* Exported by the reference library but absent from its header. */
+/* src/rpl_quantization.c:77-91 */
+QuantizedTensor* tensor_quantize_int8_symmetric(const Tensor* input);
+/* src/rpl_quantization.c:93-107 */
+QuantizedTensor* tensor_quantize_int8_asymmetric(const Tensor* input);
+/* src/rpl_quantization.c:120-160; channel_axis only selects num_channels = shape[axis] */
+PerChannelQuantizedTensor* tensor_quantize_per_channel(const Tensor* input, uint32_t channel_axis);
+/* src/rpl_quantization.c:162-168 */
+void    per_channel_quantized_tensor_free(PerChannelQuantizedTensor* qt);
+/* src/rpl_quantization.c:314-353; only ->data of the three tensors is read */
+void    linear_int8(const QuantizedTensor* input, const QuantizedTensor* weight, const QuantizedTensor* bias,
+                    int32_t* output, uint32_t batch_size, uint32_t in_features, uint32_t out_features);
+/* src/rpl_quantization.c:26-71 */
+QuantizationCalibrator* calibrator_create(void);
+void    calibrator_update(QuantizationCalibrator* cal, const Tensor* t);
+void    calibrator_compute_params(QuantizationCalibrator* cal, bool symmetric);
+void    calibrator_free(QuantizationCalibrator* cal);
+/* src/rpl_quantization.c:278-307 (per_channel is accepted and ignored, as there) */
+QuantizedModel* model_quantize(Tensor** parameters, uint32_t num_params, bool per_channel);
+void    quantized_model_free(QuantizedModel* qm);
+/* include/rpl.h:123, src/rpl_core.c:223-262 (ReLU between quantized layers) */
+void    tensor_relu_inplace(Tensor* t);
+
+/* ------------------------------------------------------------------------
+ * Additions in the reference's style (no counterpart there).
+ * ---------------------------------------------------------------------- */
+/* Last failure of a reference-named call on this thread: 0 or an RPLB_E_* /
+ * cudaError_t value.  Those calls cannot return errors through their
+ * signatures; like the reference's accelerator file they print one line to
+ * stderr and return (NULL for producers). */
+int     rpl_cuda_last_error(void);
+
+/* A Tensor whose data lives in device memory (device = DEVICE_GPU); release
+ * with tensor_free.  tensor_upload copies a host tensor to a new device one,
+ * tensor_download the other way. */
+Tensor* tensor_create_device(uint32_t dims, const uint32_t* shape);
+Tensor* tensor_upload(const Tensor* host);
+Tensor* tensor_download(const Tensor* dev);
+
+/* out[m,n] = relu?( ((float)acc * x->scale) * w->scales[n] + bias[n] ) with acc
+ * as linear_int8 computes it: x [batch, in], w [out, in] quantized per output
+ * row, bias fp32 [out] or NULL, out fp32 [batch, out].  Pointers host or
+ * device, each on its own. */
+void    linear_int8_dequant(const QuantizedTensor* x, const PerChannelQuantizedTensor* w, const float* bias,
+                            float* out, uint32_t batch_size, uint32_t in_features, uint32_t out_features,
+                            bool relu);
+
+/* out = (float)q * scales[channel], a new fp32 Tensor shaped like the input. */
+Tensor* tensor_dequantize_per_channel(const PerChannelQuantizedTensor* input);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RPL_B200_H */

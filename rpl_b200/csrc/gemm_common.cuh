@@ -1,0 +1,61 @@
+// What the two contraction kernels (dp4a and tcgen05) share: the description of
+// a problem and the three epilogues of the path.
+#pragma once
+#include "common.cuh"
+
+namespace rplb {
+
+enum EpilogueMode : int {
+    EPI_RAW_I32 = 0,      // linear_int8: raw accumulator (+ int8 bias)      src/rpl_quantization.c:346-350
+    EPI_REQUANT_I32 = 1,  // gemm_int8: roundf(sum*sa*sb/sc) as int32        src/ops_extended.c:119-120
+    EPI_DEQUANT_F32 = 2,  // fused fp32: ((float)acc*sA)*sW[n] + bias[n], optional ReLU
+};
+
+struct GemmProblem {
+    const int8_t* A;      // [M,K] row-major
+    const int8_t* B;      // b_is_kn ? [K,N] row-major : [N,K] row-major
+    void* out;            // int32 or float, [M, ldo]
+    uint64_t M, N, K, ldo;
+    int b_is_kn;
+    int mode;
+    // EPI_RAW_I32
+    const int8_t* bias_i8;
+    // EPI_REQUANT_I32
+    float sa, sb, sc;
+    int32_t za, zb;
+    // EPI_DEQUANT_F32
+    const float* a_scale;     // one float on the device
+    const float* w_scales;    // N floats
+    const float* bias_f32;    // N floats or null
+    int relu;
+};
+
+#ifdef __CUDACC__
+// Requantize as the scalar branch of gemm_int8_fallback does: three fp32
+// operations left to right, then roundf and the x86 float->int conversion.
+__device__ __forceinline__ int32_t requant_i32(int32_t sum, float sa, float sb, float sc) {
+    float r = __fmul_rn(__int2float_rn(sum), sa);
+    r = __fmul_rn(r, sb);
+    r = __fdiv_rn(r, sc);
+    return round_to_i32_x86(r);
+}
+
+// One output value of the fused fp32 epilogue; each step is rounded on its own
+// (no fused multiply-add), in the order the CPU restatement uses.
+__device__ __forceinline__ float dequant_f32(int32_t acc, float a_scale, float w_scale, bool has_bias,
+                                             float bias, bool relu) {
+    float v = __fmul_rn(__int2float_rn(acc), a_scale);
+    v = __fmul_rn(v, w_scale);
+    if (has_bias) v = __fadd_rn(v, bias);
+    if (relu && v < 0.0f) v = 0.0f;
+    return v;
+}
+#endif
+
+// Implemented in gemm_i8_simt.cu / gemm_i8_tcgen05.cu.
+int gemm_simt(const GemmProblem& p, cudaStream_t st);
+int gemm_tcgen05(const GemmProblem& p, cudaStream_t st);
+// True when the tensor-core kernel can take the problem as it stands.
+bool gemm_tcgen05_supports(const GemmProblem& p);
+
+}  // namespace rplb

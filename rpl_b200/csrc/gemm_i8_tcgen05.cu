@@ -1,0 +1,465 @@
+// INT8 x INT8 -> INT32 contraction on the 5th-generation tensor cores.
+//
+// C[m,n] = sum_k A[m,k] * W[n,k], A [M,K] and W [N,K] both K-contiguous
+// (the layout of linear_int8, src/rpl_quantization.c:340-343), followed by one
+// of the three epilogues of the path.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor.2d loads of a 128 x 128-byte
+//               A tile and a 256 x 128-byte W tile per stage, 128-byte swizzle,
+//               no multicast; kStages-deep ring of shared-memory stages.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8
+//               (128 x 256 x 32 per instruction, four per stage) into one of two
+//               256-column TMEM accumulators, and tcgen05.commit to hand stages
+//               back to the producer and finished accumulators to the epilogue.
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, apply the
+//               epilogue in registers, store to global memory.  While they drain
+//               one accumulator the MMA warp fills the other.
+//
+// Every wait on an mbarrier is bounded: when the limit passes the waiter writes
+// a code to a status word in global memory and raises a CTA-wide abort flag,
+// all roles leave their loops, TMEM is released and the kernel returns; the
+// host turns the status word into RPLB_E_KERNEL.
+#include "gemm_common.cuh"
+#include <cuda.h>
+#include <mutex>
+
+namespace rplb {
+
+constexpr int TILE_M = 128;          // rows of A per tile = TMEM lanes
+constexpr int TILE_N = 256;          // rows of W per tile = accumulator columns
+constexpr int TILE_K = 128;          // bytes of K per stage = one 128-byte swizzle row
+constexpr int MMA_K = 32;            // K per tcgen05.mma.kind::i8
+constexpr int kStages = 4;
+constexpr int kAccBuffers = 2;
+constexpr int kTmemCols = 512;       // 2 x 256 int32 columns: all of TMEM
+constexpr int TC_THREADS = 192;
+constexpr int kEpilogueWarp0 = 2;
+constexpr int kEpilogueThreads = 128;
+constexpr uint32_t A_STAGE_BYTES = TILE_M * TILE_K;      // 16 KiB
+constexpr uint32_t B_STAGE_BYTES = TILE_N * TILE_K;      // 32 KiB
+constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GROUP_M = 16;          // m-tiles per rasterisation group (L2 reuse of W tiles)
+
+// Dynamic shared memory, after alignment to 1024 bytes:
+//   [kStages][A tile | W tile]   then the block below.
+struct __align__(16) TcShared {
+    uint64_t full[kStages];          // producer -> MMA: stage loaded
+    uint64_t empty[kStages];         // MMA -> producer: stage consumed
+    uint64_t acc_full[kAccBuffers];  // MMA -> epilogue: accumulator complete
+    uint64_t acc_empty[kAccBuffers]; // epilogue -> MMA: accumulator drained
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float w_scales[4 * TILE_N];      // per-tile copies for the fp32 epilogue, one per epilogue warp
+    float bias[4 * TILE_N];
+};
+constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)kStages * STAGE_BYTES + sizeof(TcShared);
+
+// Status codes written to the status word when a wait gives up.
+enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4 };
+
+// --------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with the given parity.  Gives up after about a second
+// (or as soon as another role has given up) and returns false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, TcShared* sh, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            if (sh->abort_flag) return false;
+            if (clock64() - t0 > 2000000000LL) {
+                sh->abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane
+// (base lane + i), registers 0..31 = columns.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// stored with the 128-byte swizzle in 1024-byte atoms of 8 rows:
+//   bits  0-13  start address >> 4
+//   bits 16-29  leading byte offset >> 4 (not used by swizzled K-major layouts; 1)
+//   bits 32-45  stride byte offset >> 4  = 1024 >> 4 (distance between 8-row groups)
+//   bits 46-47  descriptor version = 1
+//   bits 61-63  layout = 2 (128-byte swizzle)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: dense, no saturation, int32 accumulator (2 << 4),
+// A and B signed int8 (1 << 7, 1 << 10), both K-major, N >> 3 at bit 17,
+// M >> 4 at bit 24.
+constexpr uint32_t kIdescI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+
+// Tile index -> (m-tile, n-tile): tiles are numbered so that CTAs running at the
+// same time cover GROUP_M consecutive m-tiles of a few n-tiles, which keeps the
+// set of A and W rows being streamed small enough to be served from L2.
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t& tm, uint32_t& tn) {
+    const uint32_t per_group = GROUP_M * tiles_n;
+    const uint32_t group = tile / per_group;
+    const uint32_t first_m = group * GROUP_M;
+    const uint32_t rows = min((uint32_t)GROUP_M, tiles_m - first_m);
+    const uint32_t in_group = tile - group * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+
+// --------------------------------------------------------------------------- epilogue of one 32-column chunk
+// Thread = one output row m; r[0..31] = accumulators of columns n_first..n_first+31.
+template <int MODE>
+__device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t (&r)[32], uint64_t m, uint64_t n_first,
+                                            float a_scale, const float* s_scales, const float* s_bias) {
+    if (m >= p.M) return;
+    const uint64_t n_left = p.N - n_first;          // caller guarantees n_first < N
+    if (MODE == EPI_DEQUANT_F32) {
+        float* row = static_cast<float*>(p.out) + m * p.ldo + n_first;
+        const bool has_bias = p.bias_f32 != nullptr;
+        const bool relu = p.relu != 0;
+        if (n_left >= 32 && (((uintptr_t)row & 15) == 0)) {
+            #pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+                float4 v;
+                v.x = dequant_f32((int32_t)r[c + 0], a_scale, s_scales[c + 0], has_bias, s_bias[c + 0], relu);
+                v.y = dequant_f32((int32_t)r[c + 1], a_scale, s_scales[c + 1], has_bias, s_bias[c + 1], relu);
+                v.z = dequant_f32((int32_t)r[c + 2], a_scale, s_scales[c + 2], has_bias, s_bias[c + 2], relu);
+                v.w = dequant_f32((int32_t)r[c + 3], a_scale, s_scales[c + 3], has_bias, s_bias[c + 3], relu);
+                __stcs(reinterpret_cast<float4*>(row + c), v);
+            }
+        } else {
+            #pragma unroll
+            for (int c = 0; c < 32; c++)
+                if ((uint64_t)c < n_left)
+                    row[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[c], has_bias, s_bias[c], relu);
+        }
+    } else {
+        int32_t* row = static_cast<int32_t*>(p.out) + m * p.ldo + n_first;
+        int32_t v[32];
+        #pragma unroll
+        for (int c = 0; c < 32; c++) {
+            int32_t s = (int32_t)r[c];
+            if (MODE == EPI_RAW_I32) {
+                if (p.bias_i8 && (uint64_t)c < n_left) s = (int32_t)((uint32_t)s + (uint32_t)(int32_t)__ldg(p.bias_i8 + n_first + c));
+            } else {
+                s = requant_i32(s, p.sa, p.sb, p.sc);
+            }
+            v[c] = s;
+        }
+        if (n_left >= 32 && (((uintptr_t)row & 15) == 0)) {
+            #pragma unroll
+            for (int c = 0; c < 32; c += 4)
+                __stcs(reinterpret_cast<int4*>(row + c), make_int4(v[c], v[c + 1], v[c + 2], v[c + 3]));
+        } else {
+            #pragma unroll
+            for (int c = 0; c < 32; c++)
+                if ((uint64_t)c < n_left) row[c] = v[c];
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- the kernel
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                  const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)kStages * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t total_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < kAccBuffers; a++) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], kEpilogueThreads / 32); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                uint32_t tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, sh, status, TC_WAIT_EMPTY)) { ok = false; break; }
+                    uint8_t* a_dst = smem + (size_t)stage * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_STAGE_BYTES;
+                    mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tm * TILE_M));
+                    tma_load_2d(b_dst, &map_w, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tn * TILE_N));
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                if (!mbar_wait_bounded(&sh->acc_empty[acc], acc_phase ^ 1, sh, status, TC_WAIT_ACC_EMPTY)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * TILE_N;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->full[stage], phase, sh, status, TC_WAIT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + A_STAGE_BYTES);
+                    #pragma unroll
+                    for (int k = 0; k < TILE_K / MMA_K; k++) {
+                        // Inside a 128-byte swizzle row the next K slice starts 32 bytes on: +2 in units of 16 bytes.
+                        tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (MMA_K >> 4)), b_desc + (uint64_t)(k * (MMA_K >> 4)),
+                                  kIdescI8, (kb | (uint32_t)k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&sh->empty[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(&sh->acc_full[acc]);
+                if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- epilogue
+        const uint32_t quarter = (uint32_t)warp & 3u;        // TMEM lanes this warp may read
+        const int ew = warp - kEpilogueWarp0;
+        float* s_scales = sh->w_scales + ew * TILE_N;
+        float* s_bias = sh->bias + ew * TILE_N;
+        const float a_scale = (MODE == EPI_DEQUANT_F32) ? __ldg(p.a_scale) : 0.0f;
+        uint32_t acc = 0, acc_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint32_t tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const uint64_t n0 = (uint64_t)tn * TILE_N;
+            const uint64_t m = (uint64_t)tm * TILE_M + quarter * 32 + lane;
+            if (MODE == EPI_DEQUANT_F32) {
+                __syncwarp();
+                for (int c = lane; c < TILE_N; c += 32) {
+                    const uint64_t n = n0 + c;
+                    s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
+                    s_bias[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
+                }
+                __syncwarp();
+            }
+            bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, sh, status, TC_WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            #pragma unroll 1
+            for (int chunk = 0; chunk < TILE_N / 32; chunk++) {
+                const uint64_t n_first = n0 + (uint64_t)chunk * 32;
+                if (n_first >= p.N) break;
+                uint32_t r[32];
+                tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
+                tc_wait_ld();
+                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+            if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ----------------------------------------------------------------- teardown
+    if (sh->abort_flag) {
+        // Something gave up: let copies and MMAs already in flight land before
+        // shared memory and TMEM are given back.
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the
+// library does not link against libcuda directly.
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+// Map of a row-major [rows, K] int8 matrix, box = box_rows x 128 bytes, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const int8_t* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(RPLB_E_NO_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RPLB_E_BAD_ARG, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return 0;
+}
+
+bool gemm_tcgen05_supports(const GemmProblem& p) {
+    if (p.b_is_kn) return false;                                  // W must be [N,K]
+    if (p.M == 0 || p.N == 0 || p.K == 0) return false;
+    if (p.K % 16 != 0) return false;                              // TMA: row stride in multiples of 16 bytes
+    if (((uintptr_t)p.A & 15) || ((uintptr_t)p.B & 15)) return false;
+    if (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0)) return false;
+    if (p.M > 0x7fffffffull || p.N > 0x7fffffffull || p.K > 0x7fffffffull) return false;
+    const uint64_t tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
+    return tiles < 0x7fffffffull;
+}
+
+// Status word the kernel writes when a bounded wait expires: page-locked host
+// memory mapped into the device, so the host can read it without touching the
+// stream.  One word per process.
+static int* kernel_status_word() {
+    static int* word = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        if (cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+            word = static_cast<int*>(p);
+            *word = 0;
+        } else {
+            cudaGetLastError();
+        }
+    });
+    return word;
+}
+
+int gemm_tcgen05_status(bool clear) {
+    int* w = kernel_status_word();
+    if (!w) return 0;
+    int v = *reinterpret_cast<volatile int*>(w);
+    if (clear) *reinterpret_cast<volatile int*>(w) = 0;
+    return v;
+}
+
+template <int MODE>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t tiles_m,
+                     uint32_t tiles_n, uint32_t num_kb, int* status_dev, unsigned int grid, cudaStream_t st) {
+    // Opt in to more than 48 KiB of dynamic shared memory.  The attribute is
+    // per device, so it is set on every launch (a cheap host-side call).
+    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)TC_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_kernel)")) return rc;
+    gemm_i8_tc_kernel<MODE><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    return launched("gemm_i8_tc_kernel");
+}
+
+int gemm_tcgen05(const GemmProblem& p, cudaStream_t st) {
+    if (!gemm_tcgen05_supports(p))
+        return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W, zero points 0");
+    if (int prev = gemm_tcgen05_status(true))
+        return fail(RPLB_E_KERNEL, "an earlier tcgen05 GEMM gave up waiting (code %d)", prev);
+    int* status_host = kernel_status_word();
+    if (!status_host) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
+    int* status_dev = nullptr;
+    if (int rc = cuda_ok(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0), "cudaHostGetDevicePointer")) return rc;
+
+    CUtensorMap ma, mw;
+    if (int rc = make_map(&ma, p.A, p.M, p.K, TILE_M)) return rc;
+    if (int rc = make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
+    const uint32_t tiles_m = (uint32_t)((p.M + TILE_M - 1) / TILE_M);
+    const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
+    const uint32_t num_kb = (uint32_t)((p.K + TILE_K - 1) / TILE_K);
+    const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
+    unsigned int sms = (unsigned int)sm_count();
+    if (sms == 0) sms = 148;
+    const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
+    switch (p.mode) {
+        case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+        case EPI_REQUANT_I32: return launch_tc<EPI_REQUANT_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+        case EPI_DEQUANT_F32: return launch_tc<EPI_DEQUANT_F32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+    }
+    return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
+}
+
+}  // namespace rplb

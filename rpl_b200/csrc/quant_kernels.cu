@@ -1,0 +1,490 @@
+// Memory-bound kernels of the path: min/max reduction, fp32 -> int8 quantize
+// (per tensor and per channel) and int8 -> fp32 dequantize.
+//
+// Data layout: tensors are flat, contiguous, row-major.  The vector paths view
+// them as "quads": one float4 (16 B) in, one packed int8x4 word (4 B) out, or
+// the reverse.  A warp touches 32 consecutive quads per instruction, so every
+// load is 512 contiguous bytes and every store 128 (quantize) or the other way
+// round (dequantize).  Buffers whose base address does not allow that
+// (fp32 side not 16-byte aligned, int8 side not 4-byte aligned) take the
+// scalar kernels, which compute the same values.
+#include "common.cuh"
+
+namespace rplb {
+
+constexpr int kThreads = 256;       // threads per CTA in the streaming kernels
+constexpr int kUnroll = 4;          // quads per thread per grid-stride step
+constexpr int kCtasPerSm = 8;       // 2048 resident threads per SM
+
+static inline unsigned int stream_grid(uint64_t work_items, uint64_t items_per_cta) {
+    uint64_t need = (work_items + items_per_cta - 1) / items_per_cta;
+    uint64_t cap = (uint64_t)sm_count() * kCtasPerSm;
+    if (cap == 0) cap = 148 * kCtasPerSm;
+    if (need < 1) need = 1;
+    return (unsigned int)(need < cap ? need : cap);
+}
+
+// ---------------------------------------------------------------------------
+// min/max  (src/ops_extended.c:52-61, src/rpl_quantization.c:79-85)
+// ---------------------------------------------------------------------------
+// Every CTA reduces a grid-stride slice to one (min,max) pair in scratch, takes
+// a ticket, and the CTA that draws the last ticket folds the pairs and writes
+// the derived parameters.  fminf/fmaxf return the other operand when one is
+// NaN, which is what the reference's strict compares amount to (a NaN never
+// replaces the running value).
+__device__ __forceinline__ void finalize_params(float lo, float hi, float first, rplb_qparams* p) {
+    p->true_min = lo;
+    p->true_max = hi;
+    p->first = first;
+    // Seeds of src/rpl_quantization.c:79: a tensor with no element below
+    // FLT_MAX keeps the seed.
+    float mn = fminf(lo, FLT_MAX);
+    float mx = fmaxf(hi, -FLT_MAX);
+    p->min_val = mn;
+    p->max_val = mx;
+    p->scale_sym = __fdiv_rn(fmaxf(fabsf(mn), fabsf(mx)), 127.0f);
+    float range = __fsub_rn(mx, mn);
+    float sa = __fdiv_rn(range, 255.0f);
+    p->scale_asym = sa;
+    p->zp_asym = round_to_i32_x86(__fdiv_rn(-mn, sa));
+}
+
+__global__ void __launch_bounds__(kThreads)
+minmax_kernel(const float* __restrict__ x, uint64_t n, uint64_t head, uint64_t nquads,
+              float2* __restrict__ partials, unsigned int* __restrict__ ticket,
+              rplb_qparams* __restrict__ params) {
+    float lo = INFINITY, hi = -INFINITY;
+    const float4* xq = reinterpret_cast<const float4*>(x + head);
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
+    // Main body: kUnroll independent 16-byte loads in flight per thread.
+    for (; i + (kUnroll - 1) * stride < nquads; i += kUnroll * stride) {
+        float4 v[kUnroll];
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) v[u] = __ldg(xq + i + u * stride);
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            lo = fminf(fminf(lo, v[u].x), fminf(v[u].y, fminf(v[u].z, v[u].w)));
+            hi = fmaxf(fmaxf(hi, v[u].x), fmaxf(v[u].y, fmaxf(v[u].z, v[u].w)));
+        }
+    }
+    for (; i < nquads; i += stride) {
+        float4 v = __ldg(xq + i);
+        lo = fminf(fminf(lo, v.x), fminf(v.y, fminf(v.z, v.w)));
+        hi = fmaxf(fmaxf(hi, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+    }
+    // Unaligned head and the tail that does not fill a quad.
+    if (blockIdx.x == 0) {
+        uint64_t tail0 = head + nquads * 4;
+        for (uint64_t j = threadIdx.x; j < head; j += kThreads) { float v = x[j]; lo = fminf(lo, v); hi = fmaxf(hi, v); }
+        for (uint64_t j = tail0 + threadIdx.x; j < n; j += kThreads) { float v = x[j]; lo = fminf(lo, v); hi = fmaxf(hi, v); }
+    }
+
+    __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+    __shared__ bool s_last;
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; }
+    __syncthreads();
+    if (warp == 0) {
+        lo = lane < kThreads / 32 ? s_lo[lane] : INFINITY;
+        hi = lane < kThreads / 32 ? s_hi[lane] : -INFINITY;
+        lo = warp_min(lo);
+        hi = warp_max(hi);
+        if (lane == 0) {
+            partials[blockIdx.x] = make_float2(lo, hi);
+            __threadfence();
+            unsigned int t = atomicAdd(ticket, 1u);
+            s_last = (t == gridDim.x - 1);
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    lo = INFINITY; hi = -INFINITY;
+    for (unsigned int j = threadIdx.x; j < gridDim.x; j += kThreads) {
+        float2 p = __ldcg(partials + j);
+        lo = fminf(lo, p.x);
+        hi = fmaxf(hi, p.y);
+    }
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kThreads / 32; w++) { lo = fminf(lo, s_lo[w]); hi = fmaxf(hi, s_hi[w]); }
+        finalize_params(lo, hi, n ? x[0] : 0.0f, params);
+        *ticket = 0;                 // leave the control word as it was found
+    }
+}
+
+// ---------------------------------------------------------------------------
+// quantize  (src/rpl_core.c:521-527)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t quantize_quad(float4 v, float scale, int32_t zp) {
+    return pack4_i8(quantize_one(v.x, scale, zp), quantize_one(v.y, scale, zp),
+                    quantize_one(v.z, scale, zp), quantize_one(v.w, scale, zp));
+}
+
+// REVERSE walks the tensor from its end: after a forward min/max pass the end
+// of the tensor is what the L2 cache still holds.
+template <bool REVERSE>
+__global__ void __launch_bounds__(kThreads)
+quantize_quads_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, uint64_t nquads,
+                      float scale_imm, int32_t zp_imm,
+                      const float* __restrict__ scale_dev, const int32_t* __restrict__ zp_dev) {
+    const float scale = scale_dev ? __ldg(scale_dev) : scale_imm;
+    const int32_t zp = zp_dev ? __ldg(zp_dev) : zp_imm;
+    // A CTA step covers kThreads*kUnroll consecutive quads; within it thread t
+    // takes quads t, t+kThreads, ... so each warp instruction is contiguous.
+    const uint64_t step = (uint64_t)kThreads * kUnroll;
+    const uint64_t nsteps = (nquads + step - 1) / step;
+    for (uint64_t s = blockIdx.x; s < nsteps; s += gridDim.x) {
+        const uint64_t base = (REVERSE ? (nsteps - 1 - s) : s) * step + threadIdx.x;
+        float4 v[kUnroll];
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nquads) v[u] = __ldcs(x + i);
+        }
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nquads) __stcs(q + i, quantize_quad(v[u], scale, zp));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+quantize_scalar_kernel(const float* __restrict__ x, int8_t* __restrict__ q, uint64_t begin, uint64_t n,
+                       float scale_imm, int32_t zp_imm,
+                       const float* __restrict__ scale_dev, const int32_t* __restrict__ zp_dev) {
+    const float scale = scale_dev ? __ldg(scale_dev) : scale_imm;
+    const int32_t zp = zp_dev ? __ldg(zp_dev) : zp_imm;
+    for (uint64_t i = begin + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kThreads)
+        q[i] = (int8_t)quantize_one(x[i], scale, zp);
+}
+
+static int launch_quantize(const float* x, int8_t* q, uint64_t n, float scale, int32_t zp,
+                           const float* scale_dev, const int32_t* zp_dev, bool reverse, cudaStream_t st) {
+    if (n == 0) return 0;
+    if (!x || !q) return fail(RPLB_E_BAD_ARG, "quantize: null pointer");
+    if ((uintptr_t)x & 3) return fail(RPLB_E_BAD_ARG, "quantize: fp32 input not 4-byte aligned");
+    const bool vec = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
+    uint64_t nquads = vec ? n / 4 : 0;
+    if (nquads) {
+        unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+        if (reverse)
+            quantize_quads_kernel<true><<<grid, kThreads, 0, st>>>((const float4*)x, (uint32_t*)q, nquads, scale, zp, scale_dev, zp_dev);
+        else
+            quantize_quads_kernel<false><<<grid, kThreads, 0, st>>>((const float4*)x, (uint32_t*)q, nquads, scale, zp, scale_dev, zp_dev);
+        if (int rc = launched("quantize_quads_kernel")) return rc;
+    }
+    if (nquads * 4 < n) {
+        uint64_t rest = n - nquads * 4;
+        unsigned int grid = stream_grid(rest, kThreads);
+        quantize_scalar_kernel<<<grid, kThreads, 0, st>>>(x, q, nquads * 4, n, scale, zp, scale_dev, zp_dev);
+        if (int rc = launched("quantize_scalar_kernel")) return rc;
+    }
+    return 0;
+}
+
+static int launch_minmax(const float* x, uint64_t n, rplb_qparams* params, cudaStream_t st) {
+    if (!params) return fail(RPLB_E_BAD_ARG, "minmax: null params pointer");
+    if (n && !x) return fail(RPLB_E_BAD_ARG, "minmax: null input");
+    if ((uintptr_t)x & 3) return fail(RPLB_E_BAD_ARG, "minmax: fp32 input not 4-byte aligned");
+    uint64_t head = (16 - ((uintptr_t)x & 15)) & 15;
+    head /= 4;
+    if (head > n) head = n;
+    uint64_t nquads = (n - head) / 4;
+    unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+    Scratch sc;
+    if (int rc = scratch_for(st, (size_t)grid * sizeof(float2), &sc)) return rc;
+    minmax_kernel<<<grid, kThreads, 0, st>>>(x, n, head, nquads, (float2*)sc.data, sc.control, params);
+    return launched("minmax_kernel");
+}
+
+
+// ---------------------------------------------------------------------------
+// per-channel quantize  (src/rpl_quantization.c:134-157)
+// ---------------------------------------------------------------------------
+// One CTA per channel (a contiguous run of channel_size floats).  Rows of up to
+// kThreads*4*kRowQuads floats are held in registers between the absmax
+// reduction and the quantize step, so HBM sees each element once; longer rows
+// are read a second time (from L2 when the row fits there).
+constexpr int kRowQuads = 8;       // float4 per thread kept in registers -> rows up to 8192 floats
+
+__device__ __forceinline__ void block_minmax(float& lo, float& hi, float* s_lo, float* s_hi) {
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; }
+    __syncthreads();
+    lo = s_lo[0]; hi = s_hi[0];
+    #pragma unroll
+    for (int w = 1; w < kThreads / 32; w++) { lo = fminf(lo, s_lo[w]); hi = fmaxf(hi, s_hi[w]); }
+}
+
+// Scale of one channel from its min/max, as src/rpl_quantization.c:136-147.
+__device__ __forceinline__ float channel_scale(float lo, float hi) {
+    float mn = fminf(lo, FLT_MAX), mx = fmaxf(hi, -FLT_MAX);
+    return __fdiv_rn(fmaxf(fabsf(mn), fabsf(mx)), 127.0f);
+}
+
+template <int QUADS>
+__global__ void __launch_bounds__(kThreads)
+per_channel_regs_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
+                        int32_t* __restrict__ zps, uint64_t num_channels, uint32_t row_quads) {
+    __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+    for (uint64_t c = blockIdx.x; c < num_channels; c += gridDim.x) {
+        const float4* row = reinterpret_cast<const float4*>(x) + c * row_quads;
+        uint32_t* out = reinterpret_cast<uint32_t*>(q) + c * row_quads;
+        float4 v[QUADS];
+        float lo = INFINITY, hi = -INFINITY;
+        #pragma unroll
+        for (int u = 0; u < QUADS; u++) {
+            uint32_t i = threadIdx.x + u * kThreads;
+            if (i < row_quads) v[u] = __ldcs(row + i);
+        }
+        #pragma unroll
+        for (int u = 0; u < QUADS; u++) {
+            uint32_t i = threadIdx.x + u * kThreads;
+            if (i < row_quads) {
+                lo = fminf(fminf(lo, v[u].x), fminf(v[u].y, fminf(v[u].z, v[u].w)));
+                hi = fmaxf(fmaxf(hi, v[u].x), fmaxf(v[u].y, fmaxf(v[u].z, v[u].w)));
+            }
+        }
+        block_minmax(lo, hi, s_lo, s_hi);
+        const float scale = channel_scale(lo, hi);
+        if (threadIdx.x == 0) { scales[c] = scale; if (zps) zps[c] = 0; }
+        #pragma unroll
+        for (int u = 0; u < QUADS; u++) {
+            uint32_t i = threadIdx.x + u * kThreads;
+            if (i < row_quads) __stcs(out + i, quantize_quad(v[u], scale, 0));
+        }
+        __syncthreads();      // s_lo/s_hi are reused by the next channel
+    }
+}
+
+// Any row length and alignment: two passes over the row, scalar accesses.
+__global__ void __launch_bounds__(kThreads)
+per_channel_stream_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scales,
+                          int32_t* __restrict__ zps, uint64_t num_channels, uint64_t channel_size, int vec) {
+    __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+    for (uint64_t c = blockIdx.x; c < num_channels; c += gridDim.x) {
+        const float* row = x + c * channel_size;
+        int8_t* out = q + c * channel_size;
+        float lo = INFINITY, hi = -INFINITY;
+        if (vec) {
+            const float4* r4 = reinterpret_cast<const float4*>(row);
+            const uint64_t nq = channel_size / 4;
+            for (uint64_t i = threadIdx.x; i < nq; i += kThreads) {
+                float4 v = __ldg(r4 + i);
+                lo = fminf(fminf(lo, v.x), fminf(v.y, fminf(v.z, v.w)));
+                hi = fmaxf(fmaxf(hi, v.x), fmaxf(v.y, fmaxf(v.z, v.w)));
+            }
+        } else {
+            for (uint64_t i = threadIdx.x; i < channel_size; i += kThreads) {
+                float v = row[i];
+                lo = fminf(lo, v);
+                hi = fmaxf(hi, v);
+            }
+        }
+        block_minmax(lo, hi, s_lo, s_hi);
+        const float scale = channel_scale(lo, hi);
+        if (threadIdx.x == 0) { scales[c] = scale; if (zps) zps[c] = 0; }
+        if (vec) {
+            const float4* r4 = reinterpret_cast<const float4*>(row);
+            uint32_t* o4 = reinterpret_cast<uint32_t*>(out);
+            const uint64_t nq = channel_size / 4;
+            // Walk back from the end of the row: the most recently read part
+            // is the most likely to be in cache still.
+            for (uint64_t k = threadIdx.x; k < nq; k += kThreads) {
+                uint64_t i = nq - 1 - k;
+                __stcs(o4 + i, quantize_quad(__ldcs(r4 + i), scale, 0));
+            }
+        } else {
+            for (uint64_t i = threadIdx.x; i < channel_size; i += kThreads)
+                out[i] = (int8_t)quantize_one(row[i], scale, 0);
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// dequantize  (src/ops_extended.c:67-70)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float4 dequant_quad(uint32_t w, float scale, int32_t zp) {
+    float4 r;
+    r.x = __fmul_rn((float)((int32_t)(int8_t)(w & 0xff) - zp), scale);
+    r.y = __fmul_rn((float)((int32_t)(int8_t)((w >> 8) & 0xff) - zp), scale);
+    r.z = __fmul_rn((float)((int32_t)(int8_t)((w >> 16) & 0xff) - zp), scale);
+    r.w = __fmul_rn((float)((int32_t)(int8_t)(w >> 24) - zp), scale);
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads)
+dequantize_quads_kernel(const uint32_t* __restrict__ q, float4* __restrict__ out, uint64_t nquads,
+                        float scale, int32_t zp) {
+    const uint64_t step = (uint64_t)kThreads * kUnroll;
+    const uint64_t nsteps = (nquads + step - 1) / step;
+    for (uint64_t s = blockIdx.x; s < nsteps; s += gridDim.x) {
+        const uint64_t base = s * step + threadIdx.x;
+        uint32_t w[kUnroll];
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nquads) w[u] = __ldcs(q + i);
+        }
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nquads) __stcs(out + i, dequant_quad(w[u], scale, zp));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dequantize_scalar_kernel(const int8_t* __restrict__ q, float* __restrict__ out, uint64_t begin, uint64_t n,
+                         float scale, int32_t zp) {
+    for (uint64_t i = begin + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kThreads)
+        out[i] = __fmul_rn((float)((int32_t)q[i] - zp), scale);
+}
+
+// Per-channel: quads never straddle a channel when channel_size % 4 == 0.
+__global__ void __launch_bounds__(kThreads)
+dequantize_pc_quads_kernel(const uint32_t* __restrict__ q, const float* __restrict__ scales,
+                           float4* __restrict__ out, uint64_t nquads, uint64_t row_quads) {
+    const uint64_t step = (uint64_t)kThreads * kUnroll;
+    const uint64_t nsteps = (nquads + step - 1) / step;
+    for (uint64_t s = blockIdx.x; s < nsteps; s += gridDim.x) {
+        const uint64_t base = s * step + threadIdx.x;
+        #pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nquads) __stcs(out + i, dequant_quad(__ldcs(q + i), __ldg(scales + i / row_quads), 0));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dequantize_pc_scalar_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                            float* __restrict__ out, uint64_t n, uint64_t channel_size) {
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kThreads)
+        out[i] = __fmul_rn((float)(int32_t)q[i], scales[i / channel_size]);
+}
+
+}  // namespace rplb
+
+namespace rplb {
+// ReLU between quantized layers (src/rpl_core.c:254-255): x < 0 -> 0, in place.
+__global__ void __launch_bounds__(kThreads)
+relu_kernel(float* __restrict__ x, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kThreads) {
+        float v = x[i];
+        if (v < 0.0f) x[i] = 0.0f;
+    }
+}
+}  // namespace rplb
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+using namespace rplb;
+
+extern "C" {
+
+int rplb_minmax_f32(const float* x, uint64_t n, rplb_qparams* params, void* stream) {
+    return launch_minmax(x, n, params, as_stream(stream));
+}
+
+int rplb_quantize_f32_i8(const float* x, int8_t* q, uint64_t n, float scale, int32_t zero_point, void* stream) {
+    return launch_quantize(x, q, n, scale, zero_point, nullptr, nullptr, false, as_stream(stream));
+}
+
+int rplb_quantize_f32_i8_dev(const float* x, int8_t* q, uint64_t n, const float* scale_dev,
+                             const int32_t* zp_dev, void* stream) {
+    if (!scale_dev) return fail(RPLB_E_BAD_ARG, "rplb_quantize_f32_i8_dev: null scale pointer");
+    return launch_quantize(x, q, n, 0.0f, 0, scale_dev, zp_dev, false, as_stream(stream));
+}
+
+int rplb_quantize_symmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream) {
+    if (int rc = launch_minmax(x, n, params, as_stream(stream))) return rc;
+    return launch_quantize(x, q, n, 0.0f, 0, &params->scale_sym, nullptr, true, as_stream(stream));
+}
+
+int rplb_quantize_asymmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream) {
+    if (int rc = launch_minmax(x, n, params, as_stream(stream))) return rc;
+    return launch_quantize(x, q, n, 0.0f, 0, &params->scale_asym, &params->zp_asym, true, as_stream(stream));
+}
+
+int rplb_quantize_per_channel_f32_i8(const float* x, int8_t* q, float* scales, int32_t* zero_points,
+                                     uint64_t num_channels, uint64_t channel_size, void* stream) {
+    if (num_channels == 0) return 0;
+    if (!x || !q || !scales) return fail(RPLB_E_BAD_ARG, "per-channel quantize: null pointer");
+    if ((uintptr_t)x & 3) return fail(RPLB_E_BAD_ARG, "per-channel quantize: fp32 input not 4-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    const bool vec = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0) && (channel_size % 4 == 0) && channel_size;
+    uint64_t cap = (uint64_t)sm_count() * kCtasPerSm * 4;
+    if (cap == 0) cap = 4096;
+    unsigned int grid = (unsigned int)(num_channels < cap ? num_channels : cap);
+    const uint64_t row_quads = channel_size / 4;
+    if (vec && row_quads <= (uint64_t)kThreads * kRowQuads) {
+        const uint32_t rq = (uint32_t)row_quads;
+        if (rq <= kThreads * 1)      per_channel_regs_kernel<1><<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, rq);
+        else if (rq <= kThreads * 2) per_channel_regs_kernel<2><<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, rq);
+        else if (rq <= kThreads * 4) per_channel_regs_kernel<4><<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, rq);
+        else                         per_channel_regs_kernel<kRowQuads><<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, rq);
+        return launched("per_channel_regs_kernel");
+    }
+    per_channel_stream_kernel<<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, channel_size, vec ? 1 : 0);
+    return launched("per_channel_stream_kernel");
+}
+
+int rplb_dequantize_i8_f32(const int8_t* q, float* out, uint64_t n, float scale, int32_t zero_point, void* stream) {
+    if (n == 0) return 0;
+    if (!q || !out) return fail(RPLB_E_BAD_ARG, "dequantize: null pointer");
+    if ((uintptr_t)out & 3) return fail(RPLB_E_BAD_ARG, "dequantize: fp32 output not 4-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    const bool vec = (((uintptr_t)out & 15) == 0) && (((uintptr_t)q & 3) == 0);
+    uint64_t nquads = vec ? n / 4 : 0;
+    if (nquads) {
+        unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+        dequantize_quads_kernel<<<grid, kThreads, 0, st>>>((const uint32_t*)q, (float4*)out, nquads, scale, zero_point);
+        if (int rc = launched("dequantize_quads_kernel")) return rc;
+    }
+    if (nquads * 4 < n) {
+        unsigned int grid = stream_grid(n - nquads * 4, kThreads);
+        dequantize_scalar_kernel<<<grid, kThreads, 0, st>>>(q, out, nquads * 4, n, scale, zero_point);
+        if (int rc = launched("dequantize_scalar_kernel")) return rc;
+    }
+    return 0;
+}
+
+int rplb_dequantize_per_channel_i8_f32(const int8_t* q, const float* scales, float* out,
+                                       uint64_t num_channels, uint64_t channel_size, void* stream) {
+    const uint64_t n = num_channels * channel_size;
+    if (n == 0) return 0;
+    if (!q || !out || !scales) return fail(RPLB_E_BAD_ARG, "per-channel dequantize: null pointer");
+    if ((uintptr_t)out & 3) return fail(RPLB_E_BAD_ARG, "per-channel dequantize: fp32 output not 4-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    const bool vec = (((uintptr_t)out & 15) == 0) && (((uintptr_t)q & 3) == 0) && (channel_size % 4 == 0);
+    if (vec) {
+        unsigned int grid = stream_grid(n / 4, (uint64_t)kThreads * kUnroll);
+        dequantize_pc_quads_kernel<<<grid, kThreads, 0, st>>>((const uint32_t*)q, scales, (float4*)out, n / 4, channel_size / 4);
+        return launched("dequantize_pc_quads_kernel");
+    }
+    unsigned int grid = stream_grid(n, kThreads);
+    dequantize_pc_scalar_kernel<<<grid, kThreads, 0, st>>>(q, scales, out, n, channel_size);
+    return launched("dequantize_pc_scalar_kernel");
+}
+
+int rplb_relu_f32_inplace(float* x, uint64_t n, void* stream) {
+    if (n == 0) return 0;
+    if (!x) return fail(RPLB_E_BAD_ARG, "relu: null pointer");
+    relu_kernel<<<stream_grid(n, kThreads * 4), kThreads, 0, as_stream(stream)>>>(x, n);
+    return launched("relu_kernel");
+}
+
+}  // extern "C"

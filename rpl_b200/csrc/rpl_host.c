@@ -1,0 +1,535 @@
+/*
+ * The reference's C API for the INT8 path, on top of the rplb_* device layer.
+ *
+ * Plain C, no CUDA headers: everything that touches the GPU goes through
+ * rpl_b200.h.  Each entry point keeps the reference's signature, allocation
+ * and ownership rules; the loops of the reference are replaced by kernel
+ * launches.  A data pointer may be ordinary host memory (staged through device
+ * buffers kept per thread), page-locked host memory (same, at full PCIe
+ * speed), or device / managed memory (used in place; results are then left in
+ * device memory too).
+ *
+ * Failures cannot be returned through these signatures.  Like the reference's
+ * accelerator file (src/rpl_gpu.c:95-111) a failing call prints one line to
+ * stderr; producers return NULL (the convention of tensor_create,
+ * src/rpl_core.c:45), void functions leave their outputs untouched, and
+ * rpl_cuda_last_error() holds the code.  There is no CPU fallback.
+ */
+#define _POSIX_C_SOURCE 200809L
+#include "rpl_b200.h"
+#include <float.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+int rplb_kernel_status(int clear);
+int rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
+
+#if defined(RPL_B200_OWN_TYPES)
+_Static_assert(sizeof(Tensor) == 152, "Tensor layout differs from the reference");
+_Static_assert(offsetof(Tensor, size) == 84, "Tensor.size offset");
+_Static_assert(offsetof(Tensor, _allocation) == 96, "Tensor._allocation offset");
+_Static_assert(offsetof(Tensor, device) == 112, "Tensor.device offset");
+_Static_assert(offsetof(Tensor, gpu_buffer) == 116, "Tensor.gpu_buffer offset");
+_Static_assert(offsetof(Tensor, is_leaf) == 120, "Tensor.is_leaf offset");
+_Static_assert(offsetof(Tensor, backward_fn) == 144, "Tensor.backward_fn offset");
+_Static_assert(sizeof(QuantizedTensor) == 56, "QuantizedTensor layout differs from the reference");
+_Static_assert(offsetof(QuantizedTensor, scale) == 8, "QuantizedTensor.scale offset");
+_Static_assert(offsetof(QuantizedTensor, shape) == 24, "QuantizedTensor.shape offset");
+#endif
+
+static __thread int t_last_error = 0;
+
+static int report(int rc, const char* where) {
+    if (rc != 0) {
+        t_last_error = rc;
+        fprintf(stderr, "rpl (cuda): %s failed: %s [%d]\n", where, rplb_last_error(), rc);
+    }
+    return rc;
+}
+
+int rpl_cuda_last_error(void) { return t_last_error; }
+
+/* Waits for the default stream and picks up a kernel-side give-up, if any. */
+static int finish(const char* where) {
+    int rc = rplb_stream_sync(NULL);
+    if (rc == 0) {
+        int st = rplb_kernel_status(1);
+        if (st != 0) {
+            t_last_error = RPLB_E_KERNEL;
+            fprintf(stderr, "rpl (cuda): %s: a kernel gave up waiting (code %d)\n", where, st);
+            return RPLB_E_KERNEL;
+        }
+        return 0;
+    }
+    return report(rc, where);
+}
+
+static int on_device(const void* p) { return rplb_pointer_kind(p) >= 2; }
+
+/* ------------------------------------------------------------------------
+ * Per-thread device staging buffers for host-resident arguments (grow-only).
+ * ---------------------------------------------------------------------- */
+#define STAGE_SLOTS 4
+static __thread void*  t_stage[STAGE_SLOTS];
+static __thread size_t t_stage_cap[STAGE_SLOTS];
+
+static void* stage(int slot, size_t bytes) {
+    if (bytes == 0) bytes = 16;
+    if (t_stage_cap[slot] < bytes) {
+        if (t_stage[slot]) { rplb_stream_sync(NULL); rplb_free(t_stage[slot]); }
+        t_stage[slot] = NULL;
+        t_stage_cap[slot] = 0;
+        if (report(rplb_malloc(&t_stage[slot], bytes), "staging allocation") != 0) return NULL;
+        t_stage_cap[slot] = bytes;
+    }
+    return t_stage[slot];
+}
+
+/* Device view of a read-only argument: the pointer itself when it is device
+ * memory, else a staged copy. */
+static const void* to_device(int slot, const void* p, size_t bytes) {
+    if (p == NULL) return NULL;
+    if (on_device(p)) return p;
+    void* d = stage(slot, bytes);
+    if (!d) return NULL;
+    if (report(rplb_copy(d, p, bytes, NULL), "host to device copy") != 0) return NULL;
+    return d;
+}
+
+/* ------------------------------------------------------------------------
+ * Allocation glue: src/rpl_core.c:33-77.
+ * ---------------------------------------------------------------------- */
+void* rpitorch_aligned_alloc(size_t alignment, size_t size) {
+    void* p = NULL;
+    if (posix_memalign(&p, alignment, size) != 0) return NULL;
+    return p;
+}
+
+/* Releases host blocks with free() as the reference does, and blocks that
+ * this library placed in device memory with the device allocator. */
+void rpitorch_aligned_free(void* ptr) {
+    if (!ptr) return;
+    if (on_device(ptr)) rplb_free(ptr);
+    else free(ptr);
+}
+
+static void fill_shape(Tensor* t, uint32_t dims, const uint32_t* shape) {
+    t->dims = dims;
+    t->size = 1;
+    for (uint32_t i = 0; i < dims; i++) { t->shape[i] = shape[i]; t->size *= shape[i]; }
+    if (dims) {
+        t->strides[dims - 1] = 1;
+        for (int i = (int)dims - 2; i >= 0; i--) t->strides[i] = t->strides[i + 1] * t->shape[i + 1];
+    }
+}
+
+Tensor* tensor_create(uint32_t dims, const uint32_t* shape, bool requires_grad) {
+    Tensor* t = (Tensor*)calloc(1, sizeof(Tensor));
+    if (!t) return NULL;
+    fill_shape(t, dims, shape);
+    size_t bytes = (size_t)t->size * sizeof(float);
+    t->_allocation = rpitorch_aligned_alloc(64, bytes);
+    t->_alloc_size = bytes;
+    t->data = (float*)t->_allocation;
+    if (requires_grad) {
+        t->grad = (float*)rpitorch_aligned_alloc(64, bytes);
+        if (t->grad) memset(t->grad, 0, bytes);
+    }
+    t->requires_grad = requires_grad;
+    t->is_leaf = true;
+    return t;
+}
+
+Tensor* tensor_create_device(uint32_t dims, const uint32_t* shape) {
+    Tensor* t = (Tensor*)calloc(1, sizeof(Tensor));
+    if (!t) return NULL;
+    fill_shape(t, dims, shape);
+    size_t bytes = (size_t)t->size * sizeof(float);
+    void* d = NULL;
+    if (report(rplb_malloc(&d, bytes), "tensor_create_device") != 0) { free(t); return NULL; }
+    t->_allocation = d;
+    t->_alloc_size = bytes;
+    t->data = (float*)d;
+    t->device = DEVICE_GPU;
+    t->is_leaf = true;
+    return t;
+}
+
+void tensor_free(Tensor* t) {
+    if (!t) return;
+    if (t->_allocation) rpitorch_aligned_free(t->_allocation);
+    if (t->grad) rpitorch_aligned_free(t->grad);
+    free(t);
+}
+
+Tensor* tensor_upload(const Tensor* host) {
+    if (!host) return NULL;
+    Tensor* d = tensor_create_device(host->dims, host->shape);
+    if (!d) return NULL;
+    if (report(rplb_copy(d->data, host->data, (size_t)host->size * 4, NULL), "tensor_upload") != 0 ||
+        finish("tensor_upload") != 0) { tensor_free(d); return NULL; }
+    return d;
+}
+
+Tensor* tensor_download(const Tensor* dev) {
+    if (!dev) return NULL;
+    Tensor* h = tensor_create(dev->dims, dev->shape, false);
+    if (!h) return NULL;
+    if (report(rplb_copy(h->data, dev->data, (size_t)dev->size * 4, NULL), "tensor_download") != 0 ||
+        finish("tensor_download") != 0) { tensor_free(h); return NULL; }
+    return h;
+}
+
+/* ------------------------------------------------------------------------
+ * Quantize / dequantize.
+ * ---------------------------------------------------------------------- */
+static QuantizedTensor* new_qt_like(const Tensor* input) {
+    QuantizedTensor* qt = (QuantizedTensor*)malloc(sizeof(QuantizedTensor));
+    if (!qt) return NULL;
+    memset(qt, 0, sizeof(*qt));
+    qt->size = input->size;
+    qt->dims = input->dims;
+    memcpy(qt->shape, input->shape, input->dims * sizeof(uint32_t));
+    return qt;
+}
+
+/* Shared body of the three per-tensor quantizers.
+ * how: 0 = caller's scale and zero point, 1 = symmetric, 2 = asymmetric. */
+static QuantizedTensor* quantize_common(const Tensor* input, int how, float scale, int32_t zp, const char* who) {
+    if (!input) return NULL;
+    t_last_error = 0;
+    const size_t n = input->size;
+    const int dev_in = on_device(input->data);
+    QuantizedTensor* qt = new_qt_like(input);
+    if (!qt) return NULL;
+
+    const float* x = (const float*)to_device(0, input->data, n * 4);
+    int8_t* q_dev = NULL;
+    void* own_q = NULL;
+    if (dev_in) {
+        if (report(rplb_malloc(&own_q, n), who) != 0) { free(qt); return NULL; }
+        q_dev = (int8_t*)own_q;
+    } else {
+        q_dev = (int8_t*)stage(1, n);
+    }
+    rplb_qparams* params = (rplb_qparams*)stage(2, sizeof(rplb_qparams));
+    if ((n && !x) || !q_dev || !params) { rplb_free(own_q); free(qt); return NULL; }
+
+    int rc;
+    if (how == 1)      rc = rplb_quantize_symmetric_f32_i8(x, q_dev, n, params, NULL);
+    else if (how == 2) rc = rplb_quantize_asymmetric_f32_i8(x, q_dev, n, params, NULL);
+    else               rc = rplb_quantize_f32_i8(x, q_dev, n, scale, zp, NULL);
+    if (report(rc, who) != 0) { rplb_free(own_q); free(qt); return NULL; }
+
+    rplb_qparams hp;
+    memset(&hp, 0, sizeof(hp));
+    if (how != 0 && report(rplb_copy(&hp, params, sizeof(hp), NULL), who) != 0) { rplb_free(own_q); free(qt); return NULL; }
+    if (dev_in) {
+        qt->data = q_dev;
+    } else {
+        qt->data = (int8_t*)rpitorch_aligned_alloc(64, n ? n : 1);
+        if (!qt->data || report(rplb_copy(qt->data, q_dev, n, NULL), who) != 0) { free(qt->data); free(qt); return NULL; }
+    }
+    if (finish(who) != 0) { rpitorch_aligned_free(qt->data); free(qt); return NULL; }
+    if (how == 1)      { qt->scale = hp.scale_sym;  qt->zero_point = 0; }
+    else if (how == 2) { qt->scale = hp.scale_asym; qt->zero_point = hp.zp_asym; }
+    else               { qt->scale = scale;         qt->zero_point = zp; }
+    return qt;
+}
+
+QuantizedTensor* tensor_quantize_int8(const Tensor* input, float scale, int32_t zero_point) {
+    return quantize_common(input, 0, scale, zero_point, "tensor_quantize_int8");
+}
+
+QuantizedTensor* tensor_quantize_int8_symmetric(const Tensor* input) {
+    return quantize_common(input, 1, 0.0f, 0, "tensor_quantize_int8_symmetric");
+}
+
+QuantizedTensor* tensor_quantize_int8_asymmetric(const Tensor* input) {
+    return quantize_common(input, 2, 0.0f, 0, "tensor_quantize_int8_asymmetric");
+}
+
+void quantized_tensor_free(QuantizedTensor* qt) {
+    if (!qt) return;
+    if (qt->data) rpitorch_aligned_free(qt->data);
+    free(qt);
+}
+
+/* min/max of the device reduction, fetched to the host. */
+static int minmax_to_host(const Tensor* t, rplb_qparams* hp, const char* who) {
+    const size_t n = t->size;
+    const float* x = (const float*)to_device(0, t->data, n * 4);
+    rplb_qparams* params = (rplb_qparams*)stage(2, sizeof(rplb_qparams));
+    if ((n && !x) || !params) return -1;
+    if (report(rplb_minmax_f32(x, n, params, NULL), who) != 0) return -1;
+    if (report(rplb_copy(hp, params, sizeof(*hp), NULL), who) != 0) return -1;
+    return finish(who);
+}
+
+void tensor_get_min_max(const Tensor* t, float* min_val, float* max_val) {
+    if (!t || t->size == 0) return;                      /* src/ops_extended.c:53 */
+    t_last_error = 0;
+    rplb_qparams hp;
+    if (minmax_to_host(t, &hp, "tensor_get_min_max") != 0) return;
+    if (isnan(hp.first)) {
+        /* The reference seeds both results with data[0]; no compare against a NaN succeeds. */
+        *min_val = hp.first;
+        *max_val = hp.first;
+    } else {
+        *min_val = hp.true_min;
+        *max_val = hp.true_max;
+    }
+}
+
+Tensor* tensor_dequantize_int8(QuantizedTensor* input) {
+    if (!input) return NULL;
+    t_last_error = 0;
+    const size_t n = input->size;
+    const int dev_in = on_device(input->data);
+    Tensor* out = dev_in ? tensor_create_device(input->dims, input->shape)
+                         : tensor_create(input->dims, input->shape, false);
+    if (!out) return NULL;
+    const int8_t* q = (const int8_t*)to_device(0, input->data, n);
+    float* o_dev = dev_in ? out->data : (float*)stage(1, n * 4);
+    if ((n && !q) || !o_dev) { tensor_free(out); return NULL; }
+    if (report(rplb_dequantize_i8_f32(q, o_dev, n, input->scale, input->zero_point, NULL), "tensor_dequantize_int8") != 0) {
+        tensor_free(out);
+        return NULL;
+    }
+    if (!dev_in && report(rplb_copy(out->data, o_dev, n * 4, NULL), "tensor_dequantize_int8") != 0) { tensor_free(out); return NULL; }
+    if (finish("tensor_dequantize_int8") != 0) { tensor_free(out); return NULL; }
+    return out;
+}
+
+PerChannelQuantizedTensor* tensor_quantize_per_channel(const Tensor* input, uint32_t channel_axis) {
+    if (!input || channel_axis >= MAX_DIMS) return NULL;
+    t_last_error = 0;
+    PerChannelQuantizedTensor* qt = (PerChannelQuantizedTensor*)calloc(1, sizeof(PerChannelQuantizedTensor));
+    if (!qt) return NULL;
+    /* src/rpl_quantization.c:124-127: the axis only supplies the channel count. */
+    qt->num_channels = input->shape[channel_axis];
+    qt->channel_size = qt->num_channels ? input->size / qt->num_channels : 0;
+    qt->dims = input->dims;
+    memcpy(qt->shape, input->shape, input->dims * sizeof(uint32_t));
+    const size_t n = input->size, C = qt->num_channels;
+    const int dev_in = on_device(input->data);
+    const char* who = "tensor_quantize_per_channel";
+
+    const float* x = (const float*)to_device(0, input->data, n * 4);
+    void *q_dev = NULL, *s_dev = NULL, *z_dev = NULL;
+    if (dev_in) {
+        if (report(rplb_malloc(&q_dev, n), who) || report(rplb_malloc(&s_dev, C * 4), who) || report(rplb_malloc(&z_dev, C * 4), who)) goto fail;
+    } else {
+        q_dev = stage(1, n);
+        s_dev = stage(2, C * 4);
+        z_dev = stage(3, C * 4);
+    }
+    if ((n && !x) || !q_dev || !s_dev || !z_dev) goto fail;
+    if (report(rplb_quantize_per_channel_f32_i8(x, (int8_t*)q_dev, (float*)s_dev, (int32_t*)z_dev, C, qt->channel_size, NULL), who)) goto fail;
+    if (dev_in) {
+        qt->data = (int8_t*)q_dev; qt->scales = (float*)s_dev; qt->zero_points = (int32_t*)z_dev;
+        q_dev = s_dev = z_dev = NULL;
+    } else {
+        qt->data = (int8_t*)rpitorch_aligned_alloc(64, n ? n : 1);
+        qt->scales = (float*)malloc(C ? C * 4 : 4);
+        qt->zero_points = (int32_t*)malloc(C ? C * 4 : 4);
+        if (!qt->data || !qt->scales || !qt->zero_points) goto fail;
+        if (report(rplb_copy(qt->data, q_dev, n, NULL), who) || report(rplb_copy(qt->scales, s_dev, C * 4, NULL), who) ||
+            report(rplb_copy(qt->zero_points, z_dev, C * 4, NULL), who)) goto fail;
+        q_dev = s_dev = z_dev = NULL;
+    }
+    if (finish(who) != 0) goto fail;
+    return qt;
+fail:
+    if (dev_in) { rplb_free(q_dev); rplb_free(s_dev); rplb_free(z_dev); }
+    per_channel_quantized_tensor_free(qt);
+    return NULL;
+}
+
+void per_channel_quantized_tensor_free(PerChannelQuantizedTensor* qt) {
+    if (!qt) return;
+    rpitorch_aligned_free(qt->data);
+    rpitorch_aligned_free(qt->scales);
+    rpitorch_aligned_free(qt->zero_points);
+    free(qt);
+}
+
+Tensor* tensor_dequantize_per_channel(const PerChannelQuantizedTensor* input) {
+    if (!input) return NULL;
+    t_last_error = 0;
+    const size_t C = input->num_channels, L = input->channel_size, n = C * L;
+    const int dev_in = on_device(input->data);
+    const char* who = "tensor_dequantize_per_channel";
+    Tensor* out = dev_in ? tensor_create_device(input->dims, input->shape)
+                         : tensor_create(input->dims, input->shape, false);
+    if (!out) return NULL;
+    const int8_t* q = (const int8_t*)to_device(0, input->data, n);
+    const float* s = (const float*)to_device(2, input->scales, C * 4);
+    float* o_dev = dev_in ? out->data : (float*)stage(1, n * 4);
+    if ((n && (!q || !s)) || !o_dev) { tensor_free(out); return NULL; }
+    if (report(rplb_dequantize_per_channel_i8_f32(q, s, o_dev, C, L, NULL), who) != 0) { tensor_free(out); return NULL; }
+    if (!dev_in && report(rplb_copy(out->data, o_dev, n * 4, NULL), who) != 0) { tensor_free(out); return NULL; }
+    if (finish(who) != 0) { tensor_free(out); return NULL; }
+    return out;
+}
+
+/* ------------------------------------------------------------------------
+ * INT8 contraction.
+ * ---------------------------------------------------------------------- */
+/* src/rpl_quantization.c:314-353: reads only ->data of its three tensors and
+ * writes raw int32 sums into the caller's buffer. */
+void linear_int8(const QuantizedTensor* input, const QuantizedTensor* weight, const QuantizedTensor* bias,
+                 int32_t* output, uint32_t batch_size, uint32_t in_features, uint32_t out_features) {
+    if (!input || !weight || !output) return;
+    t_last_error = 0;
+    const char* who = "linear_int8";
+    const size_t M = batch_size, K = in_features, N = out_features;
+    if (M == 0 || N == 0) return;
+    const int8_t* x = (const int8_t*)to_device(0, input->data, M * K);
+    const int8_t* w = (const int8_t*)to_device(1, weight->data, N * K);
+    const int8_t* b = bias ? (const int8_t*)to_device(2, bias->data, N) : NULL;
+    const int out_dev = on_device(output);
+    int32_t* o = out_dev ? output : (int32_t*)stage(3, M * N * 4);
+    if ((K && (!x || !w)) || (bias && !b) || !o) return;
+    if (report(rplb_linear_i8_i32(x, w, b, o, M, K, N, NULL), who) != 0) return;
+    if (!out_dev && report(rplb_copy(output, o, M * N * 4, NULL), who) != 0) return;
+    finish(who);
+}
+
+/* src/ops_extended.c:83-123, scalar branch. */
+void gemm_int8_fallback(const int8_t* A, const int8_t* B, int32_t* C, uint32_t M, uint32_t N, uint32_t K,
+                        float scale_a, float scale_b, float scale_c, int32_t zero_point_a, int32_t zero_point_b) {
+    if (!A || !B || !C) return;
+    t_last_error = 0;
+    const char* who = "gemm_int8";
+    const size_t m = M, n = N, k = K;
+    if (m == 0 || n == 0) return;
+    const int8_t* a = (const int8_t*)to_device(0, A, m * k);
+    const int8_t* b = (const int8_t*)to_device(1, B, k * n);
+    const int out_dev = on_device(C);
+    int32_t* c = out_dev ? C : (int32_t*)stage(3, m * n * 4);
+    if ((k && (!a || !b)) || !c) return;
+    if (report(rplb_gemm_i8_requant_i32(a, b, c, m, n, k, scale_a, scale_b, scale_c, zero_point_a, zero_point_b, NULL), who) != 0) return;
+    if (!out_dev && report(rplb_copy(C, c, m * n * 4, NULL), who) != 0) return;
+    finish(who);
+}
+
+/* src/ops_extended.c:124-129 */
+void gemm_int8(const int8_t* A, const int8_t* B, int32_t* C, uint32_t M, uint32_t N, uint32_t K,
+               float scale_a, float scale_b, float scale_c, int32_t zero_point_a, int32_t zero_point_b) {
+    gemm_int8_fallback(A, B, C, M, N, K, scale_a, scale_b, scale_c, zero_point_a, zero_point_b);
+}
+
+void linear_int8_dequant(const QuantizedTensor* x, const PerChannelQuantizedTensor* w, const float* bias,
+                         float* out, uint32_t batch_size, uint32_t in_features, uint32_t out_features, bool relu) {
+    if (!x || !w || !out) return;
+    t_last_error = 0;
+    const char* who = "linear_int8_dequant";
+    const size_t M = batch_size, K = in_features, N = out_features;
+    if (M == 0 || N == 0) return;
+    /* Scales and bias travel in one small staged block: [a_scale | w_scales[N] | bias[N]]. */
+    float* small = (float*)stage(2, (1 + 2 * N) * 4);
+    if (!small) return;
+    if (report(rplb_copy(small, &x->scale, 4, NULL), who) != 0) return;
+    if (report(rplb_copy(small + 1, w->scales, N * 4, NULL), who) != 0) return;
+    if (bias && report(rplb_copy(small + 1 + N, bias, N * 4, NULL), who) != 0) return;
+    const int8_t* xd = (const int8_t*)to_device(0, x->data, M * K);
+    const int8_t* wd = (const int8_t*)to_device(1, w->data, N * K);
+    const int out_dev = on_device(out);
+    float* o = out_dev ? out : (float*)stage(3, M * N * 4);
+    if ((K && (!xd || !wd)) || !o) return;
+    if (report(rplb_linear_i8_dequant_f32(xd, wd, o, M, K, N, N, small, small + 1, bias ? small + 1 + N : NULL,
+                                          relu ? 1 : 0, NULL), who) != 0) return;
+    if (!out_dev && report(rplb_copy(out, o, M * N * 4, NULL), who) != 0) return;
+    finish(who);
+}
+
+/* src/rpl_core.c:223-262 */
+void tensor_relu_inplace(Tensor* t) {
+    if (!t || t->size == 0) return;
+    t_last_error = 0;
+    const char* who = "tensor_relu_inplace";
+    const size_t n = t->size;
+    if (on_device(t->data)) {
+        if (report(rplb_relu_f32_inplace(t->data, n, NULL), who) == 0) finish(who);
+        return;
+    }
+    float* d = (float*)stage(0, n * 4);
+    if (!d) return;
+    if (report(rplb_copy(d, t->data, n * 4, NULL), who) != 0) return;
+    if (report(rplb_relu_f32_inplace(d, n, NULL), who) != 0) return;
+    if (report(rplb_copy(t->data, d, n * 4, NULL), who) != 0) return;
+    finish(who);
+}
+
+/* ------------------------------------------------------------------------
+ * Calibration and whole-model quantization: host bookkeeping over the device
+ * min/max reduction.
+ * ---------------------------------------------------------------------- */
+/* src/rpl_quantization.c:26-31 */
+QuantizationCalibrator* calibrator_create(void) {
+    QuantizationCalibrator* cal = (QuantizationCalibrator*)calloc(1, sizeof(QuantizationCalibrator));
+    if (!cal) return NULL;
+    cal->min_val = FLT_MAX;
+    cal->max_val = -FLT_MAX;
+    return cal;
+}
+
+/* src/rpl_quantization.c:33-53: running min/max over the batches seen. */
+void calibrator_update(QuantizationCalibrator* cal, const Tensor* t) {
+    if (!cal || !t) return;
+    t_last_error = 0;
+    rplb_qparams hp;
+    if (minmax_to_host(t, &hp, "calibrator_update") != 0) return;
+    if (hp.min_val < cal->min_val) cal->min_val = hp.min_val;
+    if (hp.max_val > cal->max_val) cal->max_val = hp.max_val;
+    cal->num_samples++;
+}
+
+/* (int32_t)v as the reference's x86-64 build converts it. */
+static int32_t f2i_x86(float v) {
+    if (!(fabsf(v) < 2147483648.0f)) return INT32_MIN;
+    return (int32_t)v;
+}
+
+/* src/rpl_quantization.c:55-67 */
+void calibrator_compute_params(QuantizationCalibrator* cal, bool symmetric) {
+    if (!cal) return;
+    if (symmetric) {
+        float abs_max = fmaxf(fabsf(cal->min_val), fabsf(cal->max_val));
+        cal->scale = abs_max / 127.0f;
+        cal->zero_point = 0;
+    } else {
+        float range = cal->max_val - cal->min_val;
+        cal->scale = range / 255.0f;
+        cal->zero_point = f2i_x86(roundf(-cal->min_val / cal->scale));
+    }
+}
+
+void calibrator_free(QuantizationCalibrator* cal) { free(cal); }
+
+/* src/rpl_quantization.c:278-298: every parameter is quantized per tensor,
+ * symmetric; per_channel is accepted and, as in the reference, not acted on. */
+QuantizedModel* model_quantize(Tensor** parameters, uint32_t num_params, bool per_channel) {
+    (void)per_channel;
+    QuantizedModel* qm = (QuantizedModel*)calloc(1, sizeof(QuantizedModel));
+    if (!qm) return NULL;
+    qm->num_params = num_params;
+    qm->fp32_params = parameters;
+    qm->int8_params = (QuantizedTensor**)calloc(num_params ? num_params : 1, sizeof(QuantizedTensor*));
+    if (!qm->int8_params) { free(qm); return NULL; }
+    for (uint32_t i = 0; i < num_params; i++)
+        qm->int8_params[i] = tensor_quantize_int8_symmetric(parameters[i]);
+    qm->is_quantized = true;
+    return qm;
+}
+
+/* src/rpl_quantization.c:300-307 */
+void quantized_model_free(QuantizedModel* qm) {
+    if (!qm) return;
+    for (uint32_t i = 0; i < qm->num_params; i++) quantized_tensor_free(qm->int8_params[i]);
+    free(qm->int8_params);
+    free(qm);
+}

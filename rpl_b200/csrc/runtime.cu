@@ -1,0 +1,165 @@
+// Host-side plumbing behind the rplb_* layer: error text, launch counter,
+// per-stream scratch blocks, memory and stream helpers.
+#include "common.cuh"
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
+
+namespace rplb {
+
+static thread_local char g_err_text[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err_text, sizeof(g_err_text), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    snprintf(g_err_text, sizeof(g_err_text), "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) return RPLB_E_NO_DEVICE;
+    return (int)e;
+}
+
+int launched(const char* kernel) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cuda_ok(cudaGetLastError(), kernel);
+}
+
+// ---------------------------------------------------------------------------
+struct ScratchBlock {
+    void* base = nullptr;
+    size_t bytes = 0;
+};
+static std::mutex g_scratch_mu;
+static std::map<std::pair<int, cudaStream_t>, ScratchBlock> g_scratch;
+static constexpr size_t kControlBytes = 256;
+
+int scratch_for(cudaStream_t stream, size_t bytes, Scratch* out) {
+    int dev = 0;
+    if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    ScratchBlock& b = g_scratch[std::make_pair(dev, stream)];
+    size_t want = kControlBytes + ((bytes + 255) & ~size_t(255));
+    if (b.bytes < want) {
+        if (b.base) {
+            // Work queued on the stream may still use the old block.
+            if (int rc = cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
+            cudaFree(b.base);
+            b.base = nullptr;
+            b.bytes = 0;
+        }
+        size_t grow = want < (size_t(1) << 20) ? (size_t(1) << 20) : want;
+        if (int rc = cuda_ok(cudaMalloc(&b.base, grow), "cudaMalloc(scratch)")) return rc;
+        if (int rc = cuda_ok(cudaMemsetAsync(b.base, 0, kControlBytes, stream), "cudaMemsetAsync(scratch)")) return rc;
+        b.bytes = grow;
+    }
+    out->control = static_cast<unsigned int*>(b.base);
+    out->data = static_cast<char*>(b.base) + kControlBytes;
+    return 0;
+}
+
+int sm_count() {
+    static std::mutex mu;
+    static std::map<int, int> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(dev);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+    cache[dev] = n;
+    return n;
+}
+
+}  // namespace rplb
+
+using namespace rplb;
+
+extern "C" {
+
+const char* rplb_last_error(void) { return g_err_text; }
+
+int rplb_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int rplb_device_sm_count(void) { return sm_count(); }
+
+uint64_t rplb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int rplb_malloc(void** dptr, size_t bytes) {
+    if (!dptr) return fail(RPLB_E_BAD_ARG, "rplb_malloc: null result pointer");
+    *dptr = nullptr;
+    if (bytes == 0) bytes = 1;
+    return cuda_ok(cudaMalloc(dptr, bytes), "cudaMalloc");
+}
+
+int rplb_free(void* dptr) { return dptr ? cuda_ok(cudaFree(dptr), "cudaFree") : 0; }
+
+int rplb_host_alloc(void** hptr, size_t bytes) {
+    if (!hptr) return fail(RPLB_E_BAD_ARG, "rplb_host_alloc: null result pointer");
+    *hptr = nullptr;
+    if (bytes == 0) bytes = 1;
+    return cuda_ok(cudaHostAlloc(hptr, bytes, cudaHostAllocDefault), "cudaHostAlloc");
+}
+
+int rplb_host_free(void* hptr) { return hptr ? cuda_ok(cudaFreeHost(hptr), "cudaFreeHost") : 0; }
+
+int rplb_copy(void* dst, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return 0;
+    if (!dst || !src) return fail(RPLB_E_BAD_ARG, "rplb_copy: null pointer");
+    return cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, as_stream(stream)), "cudaMemcpyAsync");
+}
+
+int rplb_stream_sync(void* stream) { return cuda_ok(cudaStreamSynchronize(as_stream(stream)), "cudaStreamSynchronize"); }
+
+int rplb_pointer_kind(const void* p) {
+    if (!p) return 0;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    switch (a.type) {
+        case cudaMemoryTypeHost: return 1;
+        case cudaMemoryTypeDevice: return 2;
+        case cudaMemoryTypeManaged: return 3;
+        default: return 0;
+    }
+}
+
+int rplb_shard_range(uint64_t n, int world, int rank, uint64_t align, uint64_t* begin, uint64_t* count) {
+    if (world <= 0 || rank < 0 || rank >= world || !begin || !count)
+        return fail(RPLB_E_BAD_ARG, "rplb_shard_range: bad world/rank");
+    if (align == 0) align = 1;
+    // Units of `align` columns are dealt out as evenly as possible, the first
+    // (units % world) ranks taking one more; the last unit may be ragged.
+    uint64_t units = (n + align - 1) / align;
+    uint64_t base = units / (uint64_t)world, extra = units % (uint64_t)world;
+    uint64_t r = (uint64_t)rank;
+    uint64_t u0 = r * base + (r < extra ? r : extra);
+    uint64_t u1 = u0 + base + (r < extra ? 1 : 0);
+    uint64_t b = u0 * align, e = u1 * align;
+    if (b > n) b = n;
+    if (e > n) e = n;
+    *begin = b;
+    *count = e - b;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,186 @@
+"""The ``rplb_*`` device-level entry points over torch CUDA tensors.
+
+torch is used here for device memory and streams only: every function passes
+``data_ptr()`` values and the current CUDA stream to ``librpl.so`` and returns
+without synchronising.  Nothing in this module computes on the host, and there
+is no fallback: a missing library or a non-CUDA tensor is an error.
+"""
+import ctypes as C
+
+import torch
+
+from . import capi
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _need(t, dtype, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError("%s must be a CUDA tensor (librpl has no CPU path)" % name)
+    if t.dtype != dtype:
+        raise TypeError("%s must be %s, got %s" % (name, dtype, t.dtype))
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    return t
+
+
+def launch_count():
+    return int(capi.load().rplb_launch_count())
+
+
+def gemm_backend(which):
+    """0 automatic, 1 dp4a kernel, 2 tcgen05 kernel; returns the previous setting."""
+    return int(capi.load().rplb_gemm_backend(int(which)))
+
+
+def kernel_status(clear=True):
+    return int(capi.load().rplb_kernel_status(1 if clear else 0))
+
+
+# --------------------------------------------------------------------------- quantize / dequantize
+def minmax(x):
+    """Device ``rplb_qparams`` (8 words) of ``x``: see ``QPARAM_*`` indices."""
+    _need(x, torch.float32, "x")
+    params = torch.empty(8, dtype=torch.float32, device=x.device)
+    capi.call("rplb_minmax_f32", _p(x), x.numel(), _p(params), _stream())
+    return params
+
+
+QPARAM_MIN, QPARAM_MAX, QPARAM_SCALE_SYM, QPARAM_SCALE_ASYM, QPARAM_ZP_ASYM = 0, 1, 2, 3, 4
+QPARAM_FIRST, QPARAM_TRUE_MIN, QPARAM_TRUE_MAX = 5, 6, 7
+
+
+def quantize(x, scale, zero_point=0, out=None):
+    """tensor_quantize_int8 with a host scale / zero point."""
+    _need(x, torch.float32, "x")
+    q = out if out is not None else torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    capi.call("rplb_quantize_f32_i8", _p(x), _p(q), x.numel(), float(scale), int(zero_point), _stream())
+    return q
+
+
+def quantize_dev(x, scale_dev, zp_dev=None, out=None):
+    """Same with the scale (and zero point) read from device memory."""
+    _need(x, torch.float32, "x")
+    q = out if out is not None else torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    capi.call("rplb_quantize_f32_i8_dev", _p(x), _p(q), x.numel(), _p(scale_dev), _p(zp_dev), _stream())
+    return q
+
+
+def quantize_symmetric(x, out=None, params=None):
+    """tensor_quantize_int8_symmetric.  Returns (q, params); the scale is
+    ``params[QPARAM_SCALE_SYM]`` and stays on the device."""
+    _need(x, torch.float32, "x")
+    q = out if out is not None else torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    if params is None:
+        params = torch.empty(8, dtype=torch.float32, device=x.device)
+    capi.call("rplb_quantize_symmetric_f32_i8", _p(x), _p(q), x.numel(), _p(params), _stream())
+    return q, params
+
+
+def quantize_asymmetric(x, out=None, params=None):
+    """tensor_quantize_int8_asymmetric.  Scale ``params[QPARAM_SCALE_ASYM]``,
+    zero point ``params.view(torch.int32)[QPARAM_ZP_ASYM]``."""
+    _need(x, torch.float32, "x")
+    q = out if out is not None else torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    if params is None:
+        params = torch.empty(8, dtype=torch.float32, device=x.device)
+    capi.call("rplb_quantize_asymmetric_f32_i8", _p(x), _p(q), x.numel(), _p(params), _stream())
+    return q, params
+
+
+def quantize_per_channel(x, num_channels=None, out=None):
+    """tensor_quantize_per_channel: channels are contiguous blocks (rows of a 2-D weight)."""
+    _need(x, torch.float32, "x")
+    Cn = int(num_channels if num_channels is not None else x.shape[0])
+    L = x.numel() // Cn if Cn else 0
+    q = out if out is not None else torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scales = torch.empty(Cn, dtype=torch.float32, device=x.device)
+    zps = torch.empty(Cn, dtype=torch.int32, device=x.device)
+    capi.call("rplb_quantize_per_channel_f32_i8", _p(x), _p(q), _p(scales), _p(zps), Cn, L, _stream())
+    return q, scales, zps
+
+
+def dequantize(q, scale, zero_point=0, out=None):
+    _need(q, torch.int8, "q")
+    o = out if out is not None else torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    capi.call("rplb_dequantize_i8_f32", _p(q), _p(o), q.numel(), float(scale), int(zero_point), _stream())
+    return o
+
+
+def dequantize_per_channel(q, scales, out=None):
+    _need(q, torch.int8, "q")
+    _need(scales, torch.float32, "scales")
+    Cn = scales.numel()
+    o = out if out is not None else torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    capi.call("rplb_dequantize_per_channel_i8_f32", _p(q), _p(scales), _p(o), Cn, q.numel() // max(Cn, 1), _stream())
+    return o
+
+
+def relu_(x):
+    _need(x, torch.float32, "x")
+    capi.call("rplb_relu_f32_inplace", _p(x), x.numel(), _stream())
+    return x
+
+
+# --------------------------------------------------------------------------- contraction
+def linear_i8(x, w, bias=None, out=None):
+    """linear_int8: x [M,K] int8, w [N,K] int8, optional int8 bias [N] -> raw int32 [M,N]."""
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError("w must be [N, K] with K = %d" % K)
+    if bias is not None:
+        _need(bias, torch.int8, "bias")
+    o = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=x.device)
+    capi.call("rplb_linear_i8_i32", _p(x), _p(w), _p(bias), _p(o), M, K, N, _stream())
+    return o
+
+
+def gemm_i8_requant(A, B, sa=1.0, sb=1.0, sc=1.0, za=0, zb=0, out=None):
+    """gemm_int8: A [M,K], B [K,N] -> int32 [M,N] = roundf(sum*sa*sb/sc)."""
+    _need(A, torch.int8, "A")
+    _need(B, torch.int8, "B")
+    M, K = A.shape
+    N = B.shape[1]
+    if B.shape[0] != K:
+        raise ValueError("B must be [K, N] with K = %d" % K)
+    o = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=A.device)
+    capi.call("rplb_gemm_i8_requant_i32", _p(A), _p(B), _p(o), M, N, K, float(sa), float(sb), float(sc),
+              int(za), int(zb), _stream())
+    return o
+
+
+def linear_i8_dequant(x, w, a_scale, w_scales, bias=None, relu=False, out=None):
+    """Fused fp32 epilogue: out = relu?(((float)acc * a_scale) * w_scales[n] + bias[n]).
+
+    ``a_scale`` is a one-element CUDA tensor (e.g. ``params[2:3]``).  ``out`` may
+    be a column block of a wider row-major matrix (its row stride is passed on).
+    """
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    if not (isinstance(a_scale, torch.Tensor) and a_scale.is_cuda and a_scale.dtype == torch.float32):
+        raise TypeError("a_scale must be a float32 CUDA tensor with one element")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError("w must be [N, K] with K = %d" % K)
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        if out.dtype != torch.float32 or not out.is_cuda or out.shape != (M, N) or out.stride(1) != 1:
+            raise ValueError("out must be a float32 CUDA [M,N] view with unit column stride")
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    capi.call("rplb_linear_i8_dequant_f32", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
+              _p(bias), 1 if relu else 0, _stream())
+    return out

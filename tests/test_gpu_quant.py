@@ -1,0 +1,156 @@
+"""Quantize / dequantize kernels against the CPU checker, bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits
+
+pytestmark = pytest.mark.gpu
+
+
+def same(a, b):
+    return np.array_equal(bits(np.asarray(a)), bits(np.asarray(b)))
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def sweep_tensor(rng, shape, sigma=3.0, outliers=1e-3):
+    x = (rng.standard_normal(shape) * sigma).astype(np.float32)
+    m = rng.random(shape) < outliers
+    x[m] = np.where(rng.random(int(m.sum())) < 0.5, -50.0, 50.0)
+    return x
+
+
+def test_golden_vectors_on_gpu(cuda, lib, golden):
+    from rpl_b200 import device as D
+    x = dev(golden["kat_x"], cuda)
+    assert same(host(D.quantize(x, 1.0, 0)), golden["kat_q_s1_z0"])
+    assert same(host(D.quantize(x, 1.0, 5)), golden["kat_q_s1_z5"])
+    assert same(host(D.dequantize(dev(golden["kat_q_s1_z5"], cuda), 1.0, 5)), golden["kat_dq_s1_z5"])
+    q, p = D.quantize_symmetric(x)
+    assert same(host(q), golden["kat_q_sym"]) and same(host(p)[D.QPARAM_SCALE_SYM], golden["kat_scale_sym"])
+    q, p = D.quantize_symmetric(dev(np.zeros(8, np.float32), cuda))
+    assert same(host(q), golden["zeros_q_sym"]) and host(p)[D.QPARAM_SCALE_SYM] == 0.0
+    odd = dev(golden["odd_x"], cuda)
+    for zp, key in ((0, "odd_q_s1_z0"), (7, "odd_q_s1_z7"), (-7, "odd_q_s1_zm7")):
+        assert same(host(D.quantize(odd, 1.0, zp)), golden[key])
+    q, p = D.quantize_symmetric(dev(golden["withnan_x"], cuda))
+    assert same(host(q), golden["withnan_q_sym"]) and same(host(p)[D.QPARAM_SCALE_SYM], golden["withnan_scale_sym"])
+    x = dev(golden["x"], cuda)
+    assert same(host(D.quantize(x, 0.05, 3)), golden["x_q_explicit"])
+    q, p = D.quantize_symmetric(x)
+    assert same(host(q), golden["x_q_sym"]) and same(host(p)[D.QPARAM_SCALE_SYM], golden["x_scale_sym"])
+    q, p = D.quantize_asymmetric(x)
+    hp = host(p)
+    assert same(host(q), golden["x_q_asym"]) and same(hp[D.QPARAM_SCALE_ASYM], golden["x_scale_asym"])
+    assert int(hp.view(np.int32)[D.QPARAM_ZP_ASYM]) == int(golden["x_zp_asym"])
+    q, sc, zp = D.quantize_per_channel(x)
+    assert same(host(q), golden["x_q_pc"]) and same(host(sc), golden["x_scales_pc"]) and same(host(zp), golden["x_zps_pc"])
+    q, sc, _ = D.quantize_per_channel(dev(golden["w"], cuda))
+    assert same(host(q), golden["w_q_pc"]) and same(host(sc), golden["w_scales_pc"])
+    assert same(host(D.dequantize(dev(golden["x_q_sym"], cuda), float(golden["x_scale_sym"]), 0)), golden["x_dq_sym"])
+    assert same(host(D.dequantize(dev(golden["x_q_asym"], cuda), float(golden["x_scale_asym"]), int(golden["x_zp_asym"]))),
+                golden["x_dq_asym"])
+    assert same(host(D.relu_(dev(golden["relu_in"], cuda))), golden["relu_out"])
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 1023, 1024, 1025, 4096 * 3 + 7, 1 << 20])
+def test_per_tensor_sizes(cuda, lib, port, n):
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(n + 1)
+    x = sweep_tensor(rng, (n,))
+    xd = dev(x, cuda)
+    for scale, zp in ((0.05, 0), (0.37, -11), (1e-3, 90)):
+        assert same(host(D.quantize(xd, scale, zp)), port.quantize(x, scale, zp))
+    q, p = D.quantize_symmetric(xd)
+    hp = host(p)
+    wq, ws = port.quantize_symmetric(x)
+    assert same(hp[D.QPARAM_SCALE_SYM], ws) and same(host(q), wq)
+    mn, mx = port.minmax_seeded(x)
+    assert same(hp[D.QPARAM_MIN], mn) and same(hp[D.QPARAM_MAX], mx)
+    q, p = D.quantize_asymmetric(xd)
+    wq, ws, wz = port.quantize_asymmetric(x)
+    hp = host(p)
+    if n:
+        assert same(host(q), wq) and same(hp[D.QPARAM_SCALE_ASYM], ws) and int(hp.view(np.int32)[D.QPARAM_ZP_ASYM]) == wz
+    qh = port.quantize(x, 0.05, 0)
+    assert same(host(D.dequantize(dev(qh, cuda), 0.05, 0)), port.dequantize(qh, 0.05, 0))
+    assert same(host(D.dequantize(dev(qh, cuda), 0.3, -17)), port.dequantize(qh, 0.3, -17))
+
+
+def test_misaligned_views_take_the_scalar_path(cuda, lib, port):
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(3)
+    x = sweep_tensor(rng, (5000,))
+    base = dev(x, cuda)
+    for off in (1, 2, 3):
+        v = base[off:off + 4001]
+        hv = x[off:off + 4001]
+        out = torch.zeros(4003, dtype=torch.int8, device=cuda)[off % 2:off % 2 + 4001]
+        assert same(host(D.quantize(v, 0.07, 2, out=out)), port.quantize(hv, 0.07, 2))
+        q, p = D.quantize_symmetric(v)
+        wq, ws = port.quantize_symmetric(hv)
+        assert same(host(q), wq) and same(host(p)[D.QPARAM_SCALE_SYM], ws)
+
+
+@pytest.mark.parametrize("shape", [(1, 4), (10, 128), (128, 784), (7, 1031), (64, 4096), (5, 8192), (3, 8196),
+                                   (2, 40000), (300, 12), (4, 1 << 18)])
+def test_per_channel_shapes(cuda, lib, port, shape):
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(shape[0] * 7919 + shape[1])
+    x = sweep_tensor(rng, shape)
+    if shape[0] > 2:
+        x[1] = 0.0                                   # an all-zero channel: scale 0, every value -128
+    q, sc, zp = D.quantize_per_channel(dev(x, cuda))
+    wq, wsc, wzp = port.quantize_per_channel(x, shape[0])
+    assert same(host(sc), wsc) and same(host(zp), wzp) and same(host(q), wq)
+    assert same(host(D.dequantize_per_channel(q, sc)), port.dequantize_per_channel(wq, wsc))
+
+
+def test_round_trip_and_idempotence_at_sweep_size(cuda, lib):
+    """2^26 elements (too slow to compare element-wise on every run against a
+    scalar CPU loop): properties that hold for any size."""
+    from rpl_b200 import device as D
+    g = torch.Generator(device=cuda)
+    g.manual_seed(11)
+    n = 1 << 26
+    x = torch.randn(n, device=cuda, generator=g) * 3.0
+    x[::1009] = 50.0
+    x[5::2003] = -50.0
+    q, p = D.quantize_symmetric(x)
+    scale = float(p[D.QPARAM_SCALE_SYM].item())
+    assert scale == float(np.float32(50.0) / np.float32(127.0))
+    assert int(q.max()) == 127 and int(q.min()) == -127
+    y = D.dequantize(q, scale, 0)
+    assert float((y - x).abs().max()) <= scale * 0.5000001
+    q2, p2 = D.quantize_symmetric(y)                 # quantizing the dequantized tensor changes nothing
+    assert torch.equal(q, q2) and float(p2[D.QPARAM_SCALE_SYM].item()) == scale
+    qc, sc, _ = D.quantize_per_channel(x.view(-1, 4096))
+    yc = D.dequantize_per_channel(qc, sc)
+    assert bool(((yc - x.view(-1, 4096)).abs() <= sc[:, None] * 0.5000001).all())
+    # explicit-scale kernel agrees with the two-pass entry point
+    assert torch.equal(D.quantize(x, scale, 0), q)
+    assert torch.equal(D.quantize_dev(x, p[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]), q)
+
+
+def test_sampled_parity_at_sweep_size(cuda, lib, port):
+    """2^26 elements: compare 64 random 4096-element windows with the checker."""
+    from rpl_b200 import device as D
+    g = torch.Generator(device=cuda)
+    g.manual_seed(12)
+    n = 1 << 26
+    x = torch.randn(n, device=cuda, generator=g) * 3.0
+    x[::997] = 50.0
+    q, p = D.quantize_symmetric(x)
+    scale = host(p)[D.QPARAM_SCALE_SYM]
+    rng = np.random.default_rng(0)
+    for start in rng.integers(0, n - 4096, 64):
+        s = int(start)
+        hx = host(x[s:s + 4096])
+        assert same(host(q[s:s + 4096]), port.quantize(hx, scale, 0))
