@@ -1,0 +1,400 @@
+"""Benchmark of the INT8 quantized-inference hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (default): the large sharded INT8 GEMM, M=65536, K=8192, N=65536.
+A is fp32 ~ N(0,1), quantized per tensor (symmetric) every step; the weight is
+fp32 ~ N(0,0.02) stored [N,K], quantized per output channel once at set-up
+(weights are static) and split over the output columns across the ranks; the
+output is fp32 acc*sA*sW[n], left column-sharded.  One step = quantize(A) +
+GEMM + dequantizing epilogue on every rank; the metric counts 2*M*N*K integer
+operations per step over the whole job ("strong" scaling: N is split).
+
+Prints one JSON line (rank 0).  `value` is timed with inputs resident in HBM;
+`e2e` repeats the step through the host-buffer API with the host->device copy
+of A and the device->host copy of the output inside the timed region.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "int8_gemm_tops_quant_gemm_dequant"
+UNIT = "TOPS"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=65536)
+    ap.add_argument("--n", type=int, default=65536)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the quantize/dequantize GB/s figures")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
+    return ap.parse_args()
+
+
+def workload_name(a):
+    if (a.m, a.n, a.k) == (65536, 65536, 8192):
+        return "large sharded INT8 GEMM M=65536 K=8192 N=65536 (A per-tensor, W per-channel, fp32 out)"
+    return "INT8 GEMM M=%d K=%d N=%d (A per-tensor, W per-channel, fp32 out)" % (a.m, a.k, a.n)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_burst": float(d["bf16_tflops"]),
+                "bf16_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU legs
+class CpuPath:
+    """The reference's CPU implementation of one step, on a bounded sample:
+    tensor_quantize_int8_symmetric on a slab of rows of A, linear_int8 of the
+    slab against a block of weight rows, fp32 scaling of the accumulators.
+    Uses oracle/_ref (the reference's own compiled code) when it is present,
+    else the C restatement."""
+
+    def __init__(self, K, target_seconds):
+        import numpy as np
+        from oracle.loader import Port, Ref, ref_available
+        self.np = np
+        self.kind = "reference" if ref_available() else "port"
+        self.impl = Ref() if self.kind == "reference" else Port()
+        self.cores = Port().num_threads()
+        self.K = K
+        rng = np.random.default_rng(0x5EED0050)
+        # Probe the host's rate on a small case, then size the sample.
+        a = rng.standard_normal((64, K)).astype(np.float32)
+        w = rng.integers(-127, 128, (1024, K), dtype=np.int8)
+        t0 = time.perf_counter()
+        q, _ = self.impl.quantize_symmetric(a)
+        self.impl.linear(q, w)
+        rate = 2.0 * 64 * 1024 * K / max(time.perf_counter() - t0, 1e-6)
+        self.cols = 8192
+        rows = int(rate * target_seconds / (2.0 * self.cols * K))
+        self.rows = max(64, min(65536, (rows // 64) * 64))
+        self.a = rng.standard_normal((self.rows, K)).astype(np.float32)
+        wf = (rng.standard_normal((self.cols, K)) * 0.02).astype(np.float32)
+        self.wq, self.ws, _ = self.impl.quantize_per_channel(wf) if self.kind == "reference" else \
+            self.impl.quantize_per_channel(wf, self.cols)
+        del wf
+        self.ops = 2.0 * self.rows * self.cols * K
+
+    def step(self):
+        np = self.np
+        q, s = self.impl.quantize_symmetric(self.a)
+        if self.kind == "reference":
+            acc = self.impl.linear(q, self.wq)
+            out = (acc.astype(np.float32) * np.float32(s)) * self.ws[None, :]
+        else:
+            out = self.impl.linear_dequant(q, self.wq, s, self.ws)
+        return out
+
+    def describe(self):
+        return ("%d rows of A x %d weight rows, K=%d: quantize(A slab) + linear_int8 + fp32 scaling of the "
+                "accumulators%s" % (self.rows, self.cols, self.K,
+                                    " (scaling done with numpy: the reference has no fused epilogue)"
+                                    if self.kind == "reference" else ""))
+
+
+def run_reference_arm(a):
+    """`--impl reference`: the reference's CPU path on the host cores, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cpu = CpuPath(a.k, max(2.0, min(a.cpu_seconds, 120.0 / max(a.steps + a.warmup, 1))))
+    for _ in range(a.warmup):
+        cpu.step()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        cpu.step()
+    dt = (time.perf_counter() - t0) / max(a.steps, 1)
+    tops = cpu.ops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": workload_name(a), "sample_per_step": cpu.describe()},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind, "sample": cpu.describe()},
+        "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def event_ms(pairs):
+    return [a.elapsed_time(b) for a, b in pairs]
+
+
+def quantize_sweep(torch, D, dev, peaks):
+    """Quantize / dequantize GB/s on 2^26 fp32 elements (256 MiB > L2), rows of 4096."""
+    n = 1 << 26
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED0040)
+    x = torch.randn(n, device=dev, generator=g) * 3.0
+    x[::1009] = 50.0
+    q = torch.empty(n, dtype=torch.int8, device=dev)
+    params = torch.empty(8, dtype=torch.float32, device=dev)
+    back = torch.empty(n, dtype=torch.float32, device=dev)
+    x2 = x.view(-1, 4096)
+    cases = [
+        ("quantize_explicit_scale", 5.0, lambda: D.quantize(x, 0.3937, 0, out=q)),
+        ("quantize_per_tensor_symmetric", 9.0, lambda: D.quantize_symmetric(x, out=q, params=params)),
+        ("minmax", 4.0, lambda: D.minmax(x)),
+        ("quantize_per_channel_rows4096", 5.0, lambda: D.quantize_per_channel(x2, out=q.view(-1, 4096))),
+        ("dequantize", 5.0, lambda: D.dequantize(q, 0.3937, 0, out=back)),
+    ]
+    res = {"elements": n, "unit": "GB/s", "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    launches = 0
+    for name, bytes_per_elem, fn in cases:
+        for _ in range(3):
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        before = D.launch_count()
+        for a, b in evs:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        launches += D.launch_count() - before
+        ms = sorted(event_ms(evs))
+        med = ms[len(ms) // 2]
+        gbs = bytes_per_elem * n / (med * 1e-3) / 1e9
+        res[name] = {"ms": med, "gbs": gbs, "bytes_per_elem": bytes_per_elem, "frac": gbs / peaks["hbm_gbs"]}
+    res["launches"] = launches
+    return res
+
+
+def smi_id(torch, dev, local):
+    """What `nvidia-smi -i` should be given for this rank's GPU."""
+    try:
+        u = str(torch.cuda.get_device_properties(dev).uuid)
+        return u if u.startswith("GPU-") else "GPU-" + u
+    except Exception:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        ids = [v for v in vis.split(",") if v]
+        return ids[local] if local < len(ids) else str(local)
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    from rpl_b200 import device as D
+    from rpl_b200.sharded import ShardedQuantizedLinear, shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: librpl has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    M, N, K = a.m, a.n, a.k
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- synthetic inputs (same A on every rank; W rows by global index) ----
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED0050)
+    A = torch.randn((M, K), device=dev, generator=g)
+    begin, count = shard_range(N, world, rank, 256)
+    wq = torch.empty((count, K), dtype=torch.int8, device=dev)
+    wsc = torch.empty(count, dtype=torch.float32, device=dev)
+    blk = 4096
+    for r0 in range(0, count, blk):
+        r1 = min(count, r0 + blk)
+        g.manual_seed(0x5EED0051 + (begin + r0))
+        w = torch.randn((r1 - r0, K), device=dev, generator=g) * 0.02
+        q, s, _ = D.quantize_per_channel(w)
+        wq[r0:r1] = q
+        wsc[r0:r1] = s
+    del w, q, s
+    layer = ShardedQuantizedLinear(wq, wsc, None, n_total=N, rank=rank, world=world)
+    out = torch.empty((M, count), dtype=torch.float32, device=dev)
+    ops_total = 2.0 * M * N * K
+    ops_rank = 2.0 * M * count * K
+
+    # ---- device-resident timing ----
+    for _ in range(max(a.warmup, 3)):
+        layer.forward(A, out=out)
+    torch.cuda.synchronize()
+    if D.kernel_status(True) != 0:
+        raise RuntimeError("the tcgen05 kernel reported an expired wait during warm-up")
+    gemm_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
+    quant_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(smi_id(torch, dev, local))
+    barrier()
+    sampler.start()
+    launches0 = D.launch_count()
+    e0.record()
+    xq, params = layer._xq, layer._params
+    a_scale = params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+    for i in range(a.steps):
+        quant_ev[i][0].record()
+        D.quantize_symmetric(A, out=xq, params=params)
+        quant_ev[i][1].record()
+        gemm_ev[i][0].record()
+        D.linear_i8_dequant(xq, wq, a_scale, wsc, None, False, out=out)
+        gemm_ev[i][1].record()
+    e1.record()
+    barrier()
+    launches = D.launch_count() - launches0
+    clocks = sampler.stop()
+    if D.kernel_status(True) != 0:
+        raise RuntimeError("the tcgen05 kernel reported an expired wait")
+    ms = e0.elapsed_time(e1) / a.steps
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    gemm_ms = sum(event_ms(gemm_ev)) / a.steps
+    quant_ms = sum(event_ms(quant_ev)) / a.steps
+
+    # ---- end to end through host buffers ----
+    e2e = None
+    if not a.no_e2e:
+        xh = torch.empty((M, K), dtype=torch.float32, pin_memory=True)
+        oh = torch.empty((M, count), dtype=torch.float32, pin_memory=True)
+        xh.copy_(A)
+        torch.cuda.synchronize()
+        layer.forward_host(xh, oh)
+        esteps = max(1, min(a.steps, 5))
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(esteps):
+            layer.forward_host(xh, oh)
+        s1.record()
+        barrier()
+        te = torch.tensor([s0.elapsed_time(s1) / esteps], device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        same = bool(torch.equal(oh[:256].to(dev), out[:256]))
+        e2e = {"value": ops_total / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(te.item()),
+               "steps": esteps, "h2d_bytes_per_step": int(M * K * 4) * world, "d2h_bytes_per_step": int(M * N * 4),
+               "api": "ShardedQuantizedLinear.forward_host (page-locked host buffers)", "matches_device_run": same}
+        del xh, oh
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    int8_peak = 2.0 * peaks["bf16_sustained"]
+    achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": ops_total / (ms_max * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+        "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": workload_name(a), "parallelism": "N-split over %d rank(s), output left column-sharded" % world,
+                   "columns_per_rank": count, "l2": "no flush: per-step inputs and outputs exceed L2 (A %.1f GiB fp32, out %.1f GiB per rank)"
+                   % (M * K * 4 / 2**30, M * count * 4 / 2**30)},
+        "breakdown_ms": {"quantize_A": quant_ms, "gemm_with_epilogue": gemm_ms},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                     "frac": achieved / int8_peak, "traffic": None, "kernel": "gemm_i8_tc_kernel",
+                     "peak_note": "2 x bf16_tflops_sustained of %s (int8 dense = 2 x bf16 dense)" % peaks["source"],
+                     "frac_of_nominal_4500": achieved / 4500.0},
+        "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
+    }
+    if world == 1 and not a.no_sweep:
+        line["quantize_sweep"] = quantize_sweep(torch, D, dev, peaks)
+    if world == 1 and not a.no_cpu:
+        del A, out
+        cpu = CpuPath(K, a.cpu_seconds)
+        cpu.step()
+        t0 = time.perf_counter()
+        cpu.step()
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": cpu.ops / dt / 1e12, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind,
+                                "sample": cpu.describe(), "seconds": dt}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference_arm(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

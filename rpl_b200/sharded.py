@@ -61,3 +61,95 @@ def global_absmax_scale(local_absmax, group=None):
     t = local_absmax.clone()
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return t / 127.0
+
+
+class ShardedQuantizedLinear:
+    """One rank's column block of a quantized Linear: ``y[:, b:b+c] = x . W[b:b+c, :]^T``.
+
+    Holds the int8 weight rows of this rank with their per-channel scales (and
+    an fp32 bias slice) in device memory.  ``forward`` quantizes the fp32
+    activation per tensor (symmetric) and runs the INT8 GEMM with the fused
+    fp32 epilogue; both are ``librpl.so`` kernels.  Mirrors the shapes of the
+    reference's ``linear_forward`` (weights ``[out, in]``, ``x . W^T + b``,
+    src/rpl_nn.c:55-77) on the INT8 path of ``linear_int8``.
+    """
+
+    def __init__(self, wq, w_scales, bias=None, n_total=None, rank=0, world=1, relu=False):
+        self.wq, self.w_scales, self.bias = wq, w_scales, bias
+        self.rank, self.world = rank, world
+        self.n_total = int(n_total if n_total is not None else wq.shape[0])
+        self.relu = relu
+        self._xq = None
+        self._params = None
+        self._dev_in = None
+        self._dev_out = None
+        self._copy_stream = None
+
+    @classmethod
+    def from_fp32(cls, w_shard, bias=None, **kw):
+        from . import device as D
+        wq, scales, _ = D.quantize_per_channel(w_shard)
+        return cls(wq, scales, bias, **kw)
+
+    def forward(self, x, out=None, row_chunks=None, after_chunk=None):
+        """x: fp32 CUDA [M,K].  Returns the fp32 column block [M, count].
+
+        ``row_chunks`` splits the GEMM into that many row blocks (same results);
+        ``after_chunk(i, r0, r1)`` is called after block i has been launched.
+        """
+        from . import device as D
+        M, K = x.shape
+        if self._xq is None or self._xq.shape != x.shape or self._xq.device != x.device:
+            self._xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+            self._params = torch.empty(8, dtype=torch.float32, device=x.device)
+        D.quantize_symmetric(x, out=self._xq, params=self._params)
+        a_scale = self._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+        count = self.wq.shape[0]
+        if out is None:
+            out = torch.empty((M, count), dtype=torch.float32, device=x.device)
+        if not row_chunks or row_chunks <= 1:
+            D.linear_i8_dequant(self._xq, self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out)
+            return out
+        step = (M + row_chunks - 1) // row_chunks
+        step = (step + 127) // 128 * 128
+        for i, r0 in enumerate(range(0, M, step)):
+            r1 = min(M, r0 + step)
+            D.linear_i8_dequant(self._xq[r0:r1], self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out[r0:r1])
+            if after_chunk is not None:
+                after_chunk(i, r0, r1)
+        return out
+
+    def forward_host(self, x_host, out_host, row_chunks=8):
+        """Host buffers in, host buffers out (page-locked for full PCIe speed).
+
+        The activation is copied to the device, quantized, and the GEMM runs in
+        row blocks; each finished block is copied back on a second stream while
+        the next one computes.  Returns after ``out_host`` is complete.
+        """
+        M, K = x_host.shape
+        dev = self.wq.device
+        if self._dev_in is None or self._dev_in.shape != x_host.shape:
+            self._dev_in = torch.empty((M, K), dtype=torch.float32, device=dev)
+            self._dev_out = torch.empty((M, self.wq.shape[0]), dtype=torch.float32, device=dev)
+            self._copy_stream = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        self._copy_stream.wait_stream(main)          # earlier readers of _dev_out are done
+        self._dev_in.copy_(x_host, non_blocking=True)
+
+        def ship(i, r0, r1):
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self._copy_stream.wait_event(ev)
+            with torch.cuda.stream(self._copy_stream):
+                out_host[r0:r1].copy_(self._dev_out[r0:r1], non_blocking=True)
+
+        self.forward(self._dev_in, out=self._dev_out, row_chunks=row_chunks, after_chunk=ship)
+        main.wait_stream(self._copy_stream)
+        main.synchronize()
+        return out_host
+
+    def gather(self, block, group=None):
+        """Full ``[M, n_total]`` output on every rank (NCCL all-gather of column blocks)."""
+        if self.world == 1:
+            return block
+        return gather_columns(block, self.n_total, self.world, group)

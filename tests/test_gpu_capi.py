@@ -1,0 +1,196 @@
+"""The reference-named C API (tensor_quantize_int8, gemm_int8, linear_int8 ...)
+called through ctypes the way a C program would, with host buffers and with
+device buffers, against the CPU checker."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits
+
+pytestmark = pytest.mark.gpu
+
+
+def same(a, b):
+    return np.array_equal(bits(np.asarray(a)), bits(np.asarray(b)))
+
+
+def host_tensor(lib, x):
+    """A library-owned host Tensor holding a copy of x."""
+    shape = (C.c_uint32 * x.ndim)(*x.shape)
+    t = lib.tensor_create(x.ndim, shape, False)
+    C.memmove(t.contents.data, np.ascontiguousarray(x).ctypes.data, x.nbytes)
+    return t
+
+
+def read_host(ptr, shape, dtype):
+    n = int(np.prod(shape))
+    buf = (C.c_char * (n * np.dtype(dtype).itemsize)).from_address(ptr)
+    return np.frombuffer(buf, dtype=dtype, count=n).reshape(shape).copy()
+
+
+def qt_view(capi, q, scale=1.0, zp=0):
+    t = capi.QuantizedTensor()
+    t.data = q.ctypes.data if isinstance(q, np.ndarray) else q.data_ptr()
+    t.scale, t.zero_point, t.size, t.dims = scale, zp, int(np.prod(q.shape)), len(q.shape)
+    for i, s in enumerate(q.shape):
+        t.shape[i] = s
+    return t
+
+
+def test_quantize_dequantize_host_buffers(cuda, lib, port):
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal((33, 257)) * 3).astype(np.float32)
+    t = host_tensor(lib, x)
+    qt = lib.tensor_quantize_int8(t, 0.05, 3)
+    assert qt and qt.contents.size == x.size and qt.contents.dims == 2 and list(qt.contents.shape[:2]) == [33, 257]
+    assert qt.contents.data % 64 == 0 and lib.rplb_pointer_kind(qt.contents.data) == 0
+    assert same(read_host(qt.contents.data, x.shape, np.int8), port.quantize(x, 0.05, 3))
+    back = lib.tensor_dequantize_int8(qt)
+    assert same(read_host(back.contents.data, x.shape, np.float32), port.dequantize(port.quantize(x, 0.05, 3), 0.05, 3))
+    lib.tensor_free(back)
+    lib.quantized_tensor_free(qt)
+
+    qs = lib.tensor_quantize_int8_symmetric(t)
+    wq, ws = port.quantize_symmetric(x)
+    assert same(np.float32(qs.contents.scale), ws) and qs.contents.zero_point == 0
+    assert same(read_host(qs.contents.data, x.shape, np.int8), wq)
+    lib.quantized_tensor_free(qs)
+
+    qa = lib.tensor_quantize_int8_asymmetric(t)
+    wq, ws, wz = port.quantize_asymmetric(x)
+    assert same(np.float32(qa.contents.scale), ws) and qa.contents.zero_point == wz
+    assert same(read_host(qa.contents.data, x.shape, np.int8), wq)
+    lib.quantized_tensor_free(qa)
+
+    mn, mx = C.c_float(), C.c_float()
+    lib.tensor_get_min_max(t, C.byref(mn), C.byref(mx))
+    assert (np.float32(mn.value), np.float32(mx.value)) == port.minmax_serial(x)
+
+    pc = lib.tensor_quantize_per_channel(t, 0)
+    wq, wsc, wzp = port.quantize_per_channel(x, 33)
+    assert pc.contents.num_channels == 33 and pc.contents.channel_size == 257
+    assert same(read_host(pc.contents.data, x.shape, np.int8), wq)
+    assert same(read_host(pc.contents.scales, (33,), np.float32), wsc)
+    assert same(read_host(pc.contents.zero_points, (33,), np.int32), wzp)
+    dq = lib.tensor_dequantize_per_channel(pc)
+    assert same(read_host(dq.contents.data, x.shape, np.float32), port.dequantize_per_channel(wq, wsc))
+    lib.tensor_free(dq)
+    lib.per_channel_quantized_tensor_free(pc)
+    assert lib.rpl_cuda_last_error() == 0
+    lib.tensor_free(t)
+
+
+def test_min_max_edge_cases(cuda, lib, port):
+    mn, mx = C.c_float(123.0), C.c_float(456.0)
+    empty = host_tensor(lib, np.zeros((0,), np.float32))
+    lib.tensor_get_min_max(empty, C.byref(mn), C.byref(mx))
+    assert (mn.value, mx.value) == (123.0, 456.0)            # untouched for size 0
+    lib.tensor_free(empty)
+    t = host_tensor(lib, np.array([np.nan, 1.0, -2.0], np.float32))
+    lib.tensor_get_min_max(t, C.byref(mn), C.byref(mx))
+    assert np.isnan(mn.value) and np.isnan(mx.value)         # seeded with a NaN first element
+    lib.tensor_free(t)
+    t = host_tensor(lib, np.array([1.0, np.nan, -2.0, 7.5], np.float32))
+    lib.tensor_get_min_max(t, C.byref(mn), C.byref(mx))
+    assert (mn.value, mx.value) == (-2.0, 7.5)
+    lib.tensor_free(t)
+
+
+def test_device_resident_tensors_stay_on_device(cuda, lib, port):
+    rng = np.random.default_rng(22)
+    x = (rng.standard_normal((16, 4096)) * 3).astype(np.float32)
+    h = host_tensor(lib, x)
+    d = lib.tensor_upload(h)
+    assert d and d.contents.device == 1 and lib.rplb_pointer_kind(d.contents.data) == 2
+    qt = lib.tensor_quantize_int8_symmetric(d)
+    assert lib.rplb_pointer_kind(qt.contents.data) == 2
+    wq, ws = port.quantize_symmetric(x)
+    assert same(np.float32(qt.contents.scale), ws)
+    back = lib.tensor_dequantize_int8(qt)
+    assert back.contents.device == 1
+    hb = lib.tensor_download(back)
+    assert same(read_host(hb.contents.data, x.shape, np.float32), port.dequantize(wq, ws, 0))
+    for t in (hb, back, d, h):
+        lib.tensor_free(t)
+    lib.quantized_tensor_free(qt)
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 128), (33, 19, 77), (300, 520, 784)])
+def test_gemm_int8_and_linear_int8_host_buffers(cuda, lib, port, mnk):
+    from rpl_b200 import capi
+    M, N, K = mnk
+    rng = np.random.default_rng(M + N)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    B = np.ascontiguousarray(W.T)
+    b = rng.integers(-128, 128, N, dtype=np.int8)
+    out = np.zeros((M, N), np.int32)
+    for fn in (lib.gemm_int8, lib.gemm_int8_fallback):
+        fn(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, N, K, 0.01, 0.01, 0.01, 0, 0)
+        assert same(out, port.gemm_requant(A, B, 0.01, 0.01, 0.01))
+    lib.gemm_int8(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, N, K, 0.013, 0.021, 0.37, 3, -7)
+    assert same(out, port.gemm_requant(A, B, 0.013, 0.021, 0.37, 3, -7))
+    qa, qw, qb = qt_view(capi, A), qt_view(capi, W), qt_view(capi, b)
+    lib.linear_int8(C.byref(qa), C.byref(qw), None, out.ctypes.data, M, K, N)
+    assert same(out, port.linear(A, W))
+    lib.linear_int8(C.byref(qa), C.byref(qw), C.byref(qb), out.ctypes.data, M, K, N)
+    assert same(out, port.linear(A, W, b))
+    assert lib.rpl_cuda_last_error() == 0
+
+
+def test_linear_int8_dequant_mixed_residency(cuda, lib, port):
+    """Weights resident on the device, activations and output in host memory."""
+    from rpl_b200 import capi
+    M, N, K = 200, 128, 784
+    rng = np.random.default_rng(5)
+    x = rng.random((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    wq, wsc, _ = port.quantize_per_channel(w, N)
+    xq, xs = port.quantize_symmetric(x)
+    wq_dev = torch.from_numpy(wq).to(cuda)
+    pc = capi.PerChannelQuantizedTensor()
+    pc.data, pc.scales = wq_dev.data_ptr(), wsc.ctypes.data
+    pc.num_channels, pc.channel_size, pc.dims = N, K, 2
+    qx = qt_view(capi, xq, float(xs))
+    out = np.zeros((M, N), np.float32)
+    lib.linear_int8_dequant(C.byref(qx), C.byref(pc), bias.ctypes.data, out.ctypes.data, M, K, N, True)
+    assert same(out, port.linear_dequant(xq, wq, xs, wsc, bias, True))
+    assert lib.rpl_cuda_last_error() == 0
+
+
+def test_calibrator_and_model_quantize(cuda, lib, port):
+    from rpl_b200 import capi
+    rng = np.random.default_rng(8)
+    batches = [(rng.standard_normal((64, 100)) * s).astype(np.float32) for s in (1.0, 4.0, 0.5)]
+    cal = lib.calibrator_create()
+    for b in batches:
+        t = host_tensor(lib, b)
+        lib.calibrator_update(cal, t)
+        lib.tensor_free(t)
+    allx = np.concatenate([b.ravel() for b in batches])
+    assert cal.contents.num_samples == 3
+    assert (np.float32(cal.contents.min_val), np.float32(cal.contents.max_val)) == port.minmax_seeded(allx)
+    lib.calibrator_compute_params(cal, True)
+    assert same(np.float32(cal.contents.scale), port.scale_symmetric(*port.minmax_seeded(allx)))
+    lib.calibrator_compute_params(cal, False)
+    s, z = port.params_asymmetric(*port.minmax_seeded(allx))
+    assert same(np.float32(cal.contents.scale), s) and cal.contents.zero_point == z
+    lib.calibrator_free(cal)
+
+    params = [host_tensor(lib, b) for b in batches]
+    arr = (C.POINTER(capi.Tensor) * 3)(*params)
+    qm = lib.model_quantize(arr, 3, True)
+    assert qm.contents.num_params == 3 and qm.contents.is_quantized
+    for i, b in enumerate(batches):
+        q = qm.contents.int8_params[i].contents
+        wq, ws = port.quantize_symmetric(b)
+        assert same(np.float32(q.scale), ws) and same(read_host(q.data, b.shape, np.int8), wq)
+    lib.quantized_model_free(qm)
+    r = host_tensor(lib, np.array([-1.0, 0.5, -0.0, 3.0], np.float32))
+    lib.tensor_relu_inplace(r)
+    assert same(read_host(r.contents.data, (4,), np.float32), port.relu(np.array([-1.0, 0.5, -0.0, 3.0], np.float32)))
+    for t in params + [r]:
+        lib.tensor_free(t)

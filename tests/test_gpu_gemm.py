@@ -1,0 +1,196 @@
+"""INT8 contraction kernels (dp4a and tcgen05) against the CPU checker:
+int32 results bit for bit, fp32 epilogue within 1e-5 relative (exact equality
+is expected and checked first)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits
+
+pytestmark = pytest.mark.gpu
+
+SIMT, TC = 1, 2
+
+
+def same(a, b):
+    return np.array_equal(bits(np.asarray(a)), bits(np.asarray(b)))
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture
+def backend():
+    from rpl_b200 import device as D
+    prev = D.gemm_backend(0)
+    yield D
+    D.gemm_backend(prev)
+    assert D.kernel_status(True) == 0
+
+
+def rel_close(got, want, tol=1e-5):
+    denom = np.maximum(np.abs(want), 1e-30)
+    return bool((np.abs(got - want) / denom <= tol).all())
+
+
+def test_golden_vectors_both_kernels(cuda, lib, golden, backend):
+    D = backend
+    A, W, b = dev(golden["A"], cuda), dev(golden["W"], cuda), dev(golden["bias_i8"], cuda)
+    B = dev(np.ascontiguousarray(golden["W"].T), cuda)
+    sa, sb, sc = (float(v) for v in golden["gemm_params"])
+    D.gemm_backend(SIMT)
+    assert same(host(D.linear_i8(A, W)), golden["linear_raw"])
+    assert same(host(D.linear_i8(A, W, b)), golden["linear_bias"])
+    assert same(host(D.gemm_i8_requant(A, B)), golden["gemm_unit"])
+    assert same(host(D.gemm_i8_requant(A, B, sa, sb, sc)), golden["gemm_scaled"])
+    assert same(host(D.gemm_i8_requant(A, B, sa, sb, sc, 3, -7)), golden["gemm_zp"])
+    two, twoT = dev(np.array([[127, 127]], np.int8), cuda), dev(np.array([[127], [127]], np.int8), cuda)
+    got = [int(D.gemm_i8_requant(two, twoT)[0, 0]), int(D.gemm_i8_requant(two, twoT, 0.5, 0.5, 2.0)[0, 0]),
+           int(D.gemm_i8_requant(two, twoT, 1, 1, 1, 3, -2)[0, 0])]
+    assert got == [32258, 4032, 31992]
+
+
+# K = 129 is not a multiple of 16, so the golden pair above cannot reach the
+# tensor-core kernel; these shapes can (K % 16 == 0), ragged M and N included.
+TC_SHAPES = [(128, 256, 128), (1, 16, 16), (37, 23, 144), (130, 300, 784), (512, 512, 512), (257, 10, 128),
+             (300, 1000, 4096), (128, 256, 16), (1000, 129, 2064)]
+
+
+@pytest.mark.parametrize("mnk", TC_SHAPES)
+def test_tcgen05_raw_and_bias(cuda, lib, port, backend, mnk):
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 31 + N * 7 + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    b = rng.integers(-128, 128, N, dtype=np.int8)
+    want = port.linear(A, W)
+    D.gemm_backend(TC)
+    got = host(D.linear_i8(dev(A, cuda), dev(W, cuda)))
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
+    assert same(got, want)
+    assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda), dev(b, cuda))), port.linear(A, W, b))
+    D.gemm_backend(SIMT)
+    assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), want)
+
+
+@pytest.mark.parametrize("mnk", [(64, 64, 64), (130, 300, 784), (512, 512, 512), (33, 77, 19), (5, 3, 1)])
+@pytest.mark.parametrize("which", [SIMT, TC])
+def test_requant_epilogue(cuda, lib, port, backend, mnk, which):
+    D = backend
+    M, N, K = mnk
+    if which == TC and K % 16:
+        pytest.skip("tensor-core kernel needs K % 16 == 0")
+    rng = np.random.default_rng(M + N + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    D.gemm_backend(which)
+    for args in ((1, 1, 1, 0, 0), (0.013, 0.021, 0.37, 0, 0), (0.5, 0.5, 1e-3, 0, 0)):
+        assert same(host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda), *args)), port.gemm_requant(A, B, *args))
+    if which == SIMT:
+        for args in ((0.013, 0.021, 0.37, 3, -7), (1, 1, 1, -128, 127), (0.3, 0.3, 1e-4, 5, 0)):
+            assert same(host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda), *args)), port.gemm_requant(A, B, *args))
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (37, 23, 144), (130, 300, 784), (256, 10, 128), (512, 512, 512)])
+@pytest.mark.parametrize("which", [SIMT, TC])
+@pytest.mark.parametrize("relu", [False, True])
+def test_fused_dequant_epilogue(cuda, lib, port, backend, mnk, which, relu):
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 3 + N * 5 + K * 7)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 2e-4).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    a_scale = np.float32(0.0231)
+    D.gemm_backend(which)
+    a_dev = dev(np.array([a_scale], np.float32), cuda)
+    for b in (bias, None):
+        want = port.linear_dequant(A, W, a_scale, ws, b, relu)
+        got = host(D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda),
+                                       dev(b, cuda) if b is not None else None, relu))
+        assert rel_close(got, want, 1e-5)
+        assert same(got, want)
+
+
+def test_fused_epilogue_writes_a_column_block_in_place(cuda, lib, port, backend):
+    """Output row stride larger than N: what an N-sharded rank does."""
+    D = backend
+    M, N, K, NT = 200, 256, 256, 768
+    rng = np.random.default_rng(9)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 1e-4).astype(np.float32)
+    want = port.linear_dequant(A, W, 0.01, ws, None, False)
+    a_dev = dev(np.array([0.01], np.float32), cuda)
+    for which in (SIMT, TC):
+        D.gemm_backend(which)
+        full = torch.full((M, NT), -7.0, device=cuda)
+        D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda), out=full[:, 256:512])
+        h = host(full)
+        assert same(h[:, 256:512], want)
+        assert (h[:, :256] == -7.0).all() and (h[:, 512:] == -7.0).all()
+
+
+def test_config1_512_cubed_end_to_end(cuda, lib, port, backend):
+    """fp32 N(0,1) 512x512 pair, per-tensor symmetric, raw / requantized / fp32 outputs."""
+    D = backend
+    rng = np.random.default_rng(0x5EED0010)
+    A = rng.standard_normal((512, 512)).astype(np.float32)
+    Bt = rng.standard_normal((512, 512)).astype(np.float32)      # stored [N,K]
+    qa, pa = D.quantize_symmetric(dev(A, cuda))
+    qb, pb = D.quantize_symmetric(dev(Bt, cuda))
+    wqa, sa = port.quantize_symmetric(A)
+    wqb, sb = port.quantize_symmetric(Bt)
+    assert same(host(qa), wqa) and same(host(qb), wqb)
+    for which in (SIMT, TC):
+        D.gemm_backend(which)
+        assert same(host(D.linear_i8(qa, qb)), port.linear(wqa, wqb))
+        Bkn = np.ascontiguousarray(wqb.T)
+        sc = np.float32(sa * sb * 64)
+        assert same(host(D.gemm_i8_requant(qa, dev(Bkn, cuda), sa, sb, sc)), port.gemm_requant(wqa, Bkn, sa, sb, sc))
+        ws = np.full(512, sb, np.float32)
+        got = host(D.linear_i8_dequant(qa, qb, pa[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], dev(ws, cuda)))
+        assert same(got, port.linear_dequant(wqa, wqb, sa, ws))
+
+
+def test_tcgen05_matches_dp4a_at_projection_size(cuda, lib, backend):
+    """4096 x 4096 x 4096 (a CPU loop would take minutes): the two kernels must
+    agree on every int32, and linearity in A must hold."""
+    D = backend
+    g = torch.Generator(device=cuda)
+    g.manual_seed(3)
+    A = torch.randint(-128, 128, (4096, 4096), device=cuda, generator=g, dtype=torch.int8)
+    W = torch.randint(-128, 128, (4096, 4096), device=cuda, generator=g, dtype=torch.int8)
+    D.gemm_backend(TC)
+    c_tc = D.linear_i8(A, W)
+    D.gemm_backend(SIMT)
+    c_simt = D.linear_i8(A, W)
+    assert torch.equal(c_tc, c_simt)
+    # column sums: sum_n C[m,n] == A[m,:] . (sum_n W[n,:])
+    colsum = W.to(torch.int64).sum(0)
+    want = (A[:64].to(torch.int64) * colsum[None, :]).sum(1)
+    assert torch.equal(c_tc[:64].to(torch.int64).sum(1), want)
+
+
+def test_sampled_tiles_vs_checker_at_projection_size(cuda, lib, port, backend):
+    D = backend
+    g = torch.Generator(device=cuda)
+    g.manual_seed(4)
+    M, N, K = 2048, 4096, 4096
+    A = torch.randint(-128, 128, (M, K), device=cuda, generator=g, dtype=torch.int8)
+    W = torch.randint(-128, 128, (N, K), device=cuda, generator=g, dtype=torch.int8)
+    D.gemm_backend(TC)
+    Cd = D.linear_i8(A, W)
+    rng = np.random.default_rng(1)
+    for _ in range(8):
+        m0, n0 = int(rng.integers(0, M - 128)), int(rng.integers(0, N - 128))
+        want = port.linear(host(A[m0:m0 + 128]), host(W[n0:n0 + 128]))
+        assert same(host(Cd[m0:m0 + 128, n0:n0 + 128]), want)
