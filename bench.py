@@ -64,7 +64,7 @@ def measured_peaks():
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -72,6 +72,8 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.lines = []
+        self.t_begin = None
+        self.t_end = None
 
     def start(self):
         try:
@@ -95,12 +97,21 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        import datetime
         sm, smax, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
+            if self.t_begin is not None and self.t_end is not None:
+                # keep only samples taken inside the timed region
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                except ValueError:
+                    continue
+                if not (self.t_begin <= ts <= self.t_end):
+                    continue
             try:
                 sm.append(float(f[1]))
                 smax = float(f[2])
@@ -299,8 +310,15 @@ def run_ours(a):
     quant_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(smi_id(torch, dev, local))
-    barrier()
+    # The sampler needs a moment to start: keep the GPU under the same load
+    # until it has, then open the timed region.
     sampler.start()
+    t_pre = time.time()
+    while time.time() - t_pre < 1.0:
+        layer.forward(A, out=out)
+        torch.cuda.synchronize()
+    barrier()
+    sampler.t_begin = time.time()
     launches0 = D.launch_count()
     e0.record()
     xq, params = layer._xq, layer._params
@@ -314,7 +332,9 @@ def run_ours(a):
         gemm_ev[i][1].record()
     e1.record()
     barrier()
+    sampler.t_end = time.time()
     launches = D.launch_count() - launches0
+    time.sleep(0.15)
     clocks = sampler.stop()
     if D.kernel_status(True) != 0:
         raise RuntimeError("the tcgen05 kernel reported an expired wait")
