@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantize/dequantize GB/s figures")
+    ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
+    ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
 
@@ -273,6 +275,9 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
     M, N, K = a.m, a.n, a.k
+    if a.sweep_only:
+        print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks)}), flush=True)
+        return
 
     def barrier():
         if world > 1:
@@ -312,11 +317,12 @@ def run_ours(a):
     sampler = ClockSampler(smi_id(torch, dev, local))
     # The sampler needs a moment to start: keep the GPU under the same load
     # until it has, then open the timed region.
-    sampler.start()
-    t_pre = time.time()
-    while time.time() - t_pre < 1.0:
-        layer.forward(A, out=out)
-        torch.cuda.synchronize()
+    if not a.no_clocks:
+        sampler.start()
+        t_pre = time.time()
+        while time.time() - t_pre < 1.0:
+            layer.forward(A, out=out)
+            torch.cuda.synchronize()
     barrier()
     sampler.t_begin = time.time()
     launches0 = D.launch_count()
