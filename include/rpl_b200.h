@@ -155,6 +155,24 @@ typedef struct {
  * Uses the library's per-stream scratch buffer (allocated on first use). */
 int  rplb_minmax_f32(const float* x, uint64_t n, rplb_qparams* params, void* stream);
 
+/* No counterpart in the reference.  rplb_minmax_f32 for callers that must not
+ * allocate device memory: plugins running inside a host application that owns
+ * the whole GPU memory budget, real-time loops where cudaMalloc's implicit
+ * synchronisation is unacceptable, code that runs after the application has
+ * frozen its allocations.  The per-CTA partial results and the ticket counter
+ * live in a fixed 8.25 KiB array that is part of the library image on every
+ * device that loads it; the call itself performs no cudaMalloc/cudaFree.
+ *   - n above RPLB_STATIC_MINMAX_MAX_ELEMENTS is rejected (RPLB_E_TOO_LARGE).
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that call before any stream capture.
+ *   - All calls share the one array: calls that may overlap on the GPU
+ *     (different streams, no ordering between them) race.  Calls ordered by a
+ *     stream or an event are safe; the counter is cleared at every call.
+ * Same inputs, outputs and results as rplb_minmax_f32. */
+#define RPLB_STATIC_MINMAX_MAX_CTAS      1024u
+#define RPLB_STATIC_MINMAX_MAX_ELEMENTS  (1ull << 30)
+int  rplb_minmax_f32_static(const float* x, uint64_t n, rplb_qparams* params, void* stream);
+
 /* Replaces the loop of tensor_quantize_int8 (src/rpl_core.c:521-527):
  * q = clamp((int32)roundf(x/scale) + zp, -128, 127). */
 int  rplb_quantize_f32_i8(const float* x, int8_t* q, uint64_t n, float scale, int32_t zero_point, void* stream);

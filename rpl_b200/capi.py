@@ -90,6 +90,7 @@ SIGNATURES = {
     "rplb_stream_sync": ("rc", [_vp]),
     "rplb_pointer_kind": (C.c_int, [_vp]),
     "rplb_minmax_f32": ("rc", [_vp, _u64, _vp, _vp]),
+    "rplb_minmax_f32_static": ("rc", [_vp, _u64, _vp, _vp]),
     "rplb_quantize_f32_i8": ("rc", [_vp, _vp, _u64, _f, _i, _vp]),
     "rplb_quantize_f32_i8_dev": ("rc", [_vp, _vp, _u64, _vp, _vp, _vp]),
     "rplb_quantize_symmetric_f32_i8": ("rc", [_vp, _vp, _u64, _vp, _vp]),

@@ -9,6 +9,7 @@
 // (fp32 side not 16-byte aligned, int8 side not 4-byte aligned) take the
 // scalar kernels, which compute the same values.
 #include "common.cuh"
+#include <mutex>
 
 namespace rplb {
 
@@ -488,3 +489,68 @@ int rplb_relu_f32_inplace(float* x, uint64_t n, void* stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free min/max
+// ---------------------------------------------------------------------------
+// Same kernel as rplb_minmax_f32, with the per-CTA partial results and the
+// ticket counter in a fixed array that is part of the loaded library image
+// instead of a cudaMalloc'ed block.
+namespace rplb {
+
+constexpr unsigned int kStaticMaxCtas = RPLB_STATIC_MINMAX_MAX_CTAS;
+
+struct StaticMinmaxScratch {
+    unsigned int ticket;                 // must be zero when the kernel starts
+    unsigned int pad[63];
+    float2 partials[kStaticMaxCtas];     // one (min, max) pair per CTA
+};
+
+// Lives in every device that loads the library, from load to exit (8.25 KiB).
+static __device__ __align__(256) StaticMinmaxScratch g_static_minmax;
+
+// Device address of the array above, per device ordinal.  In host code the
+// symbol's name is only a handle: the address a kernel can use has to be asked
+// for, with the device in question current.
+constexpr int kMaxDevices = 64;
+static StaticMinmaxScratch* g_static_minmax_addr[kMaxDevices];
+static std::mutex g_static_minmax_mu;
+
+static int static_minmax_address(StaticMinmaxScratch** out) {
+    int dev = 0;
+    if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return fail(RPLB_E_BAD_ARG, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_minmax_mu);
+    if (!g_static_minmax_addr[dev]) {
+        void* p = nullptr;
+        if (int rc = cuda_ok(cudaGetSymbolAddress(&p, g_static_minmax), "cudaGetSymbolAddress(g_static_minmax)")) return rc;
+        g_static_minmax_addr[dev] = static_cast<StaticMinmaxScratch*>(p);
+    }
+    *out = g_static_minmax_addr[dev];
+    return 0;
+}
+
+}  // namespace rplb
+
+extern "C" int rplb_minmax_f32_static(const float* x, uint64_t n, rplb_qparams* params, void* stream) {
+    using namespace rplb;
+    if (n > RPLB_STATIC_MINMAX_MAX_ELEMENTS)
+        return fail(RPLB_E_TOO_LARGE, "rplb_minmax_f32_static: %llu elements exceed the limit of %llu; use rplb_minmax_f32",
+                    (unsigned long long)n, (unsigned long long)RPLB_STATIC_MINMAX_MAX_ELEMENTS);
+    if (!params) return fail(RPLB_E_BAD_ARG, "rplb_minmax_f32_static: null params pointer");
+    if (n && !x) return fail(RPLB_E_BAD_ARG, "rplb_minmax_f32_static: null input");
+    if ((uintptr_t)x & 3) return fail(RPLB_E_BAD_ARG, "rplb_minmax_f32_static: fp32 input not 4-byte aligned");
+    cudaStream_t st = as_stream(stream);
+    StaticMinmaxScratch* sc = nullptr;
+    if (int rc = static_minmax_address(&sc)) return rc;
+    uint64_t head = ((16 - ((uintptr_t)x & 15)) & 15) / 4;
+    if (head > n) head = n;
+    const uint64_t nquads = (n - head) / 4;
+    unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+    if (grid > kStaticMaxCtas) grid = kStaticMaxCtas;       // the kernel strides over the rest
+    // Every call shares the array and it keeps what the last call left there:
+    // the ticket has to start at zero, the partials are overwritten before use.
+    if (int rc = cuda_ok(cudaMemsetAsync(&sc->ticket, 0, sizeof(unsigned int), st), "cudaMemsetAsync(ticket)")) return rc;
+    minmax_kernel<<<grid, kThreads, 0, st>>>(x, n, head, nquads, sc->partials, &sc->ticket, params);
+    return launched("minmax_kernel(static scratch)");
+}
