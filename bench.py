@@ -44,6 +44,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantize/dequantize GB/s figures")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
+    ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 single-CTA tcgen05, 4 CTA-pair tcgen05)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
 
@@ -80,7 +81,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -100,7 +101,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         import datetime
-        sm, smax, reasons = [], None, set()
+        sm, smax, reasons, watts = [], None, set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
@@ -119,12 +120,18 @@ class ClockSampler:
                 smax = float(f[2])
             except ValueError:
                 continue
+            try:
+                watts.append(float(f[3]))
+            except ValueError:
+                pass
             for name, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         sm.sort()
         med = sm[len(sm) // 2] if sm else None
-        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+        watts.sort()
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm),
+                "power_w": watts[len(watts) // 2] if watts else None}
 
 
 # --------------------------------------------------------------------------- CPU legs
@@ -275,6 +282,7 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
     M, N, K = a.m, a.n, a.k
+    D.gemm_backend(a.gemm_backend)
     if a.sweep_only:
         print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks)}), flush=True)
         return
@@ -327,14 +335,12 @@ def run_ours(a):
     sampler.t_begin = time.time()
     launches0 = D.launch_count()
     e0.record()
-    xq, params = layer._xq, layer._params
-    a_scale = params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
     for i in range(a.steps):
         quant_ev[i][0].record()
-        D.quantize_symmetric(A, out=xq, params=params)
+        xq, a_scale = layer.quantize_activation(A)
         quant_ev[i][1].record()
         gemm_ev[i][0].record()
-        D.linear_i8_dequant(xq, wq, a_scale, wsc, None, False, out=out)
+        layer.gemm(xq, a_scale, out=out)
         gemm_ev[i][1].record()
     e1.record()
     barrier()

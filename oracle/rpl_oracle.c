@@ -150,7 +150,7 @@ ORC_API void orc_quantize_per_channel(const float* x, int8_t* q, float* scales, 
 ORC_API void orc_dequantize_i8(const int8_t* q, float* out, uint64_t n, float scale, int32_t zp) {
     #pragma omp parallel for
     for (int64_t i = 0; i < (int64_t)n; i++)
-        out[i] = (float)((int32_t)q[i] - zp) * scale;
+        out[i] = (float)(int32_t)((uint32_t)(int32_t)q[i] - (uint32_t)zp) * scale;   /* int32 subtraction wraps */
 }
 
 /* Per-channel form of the same statement (the reference has no per-channel

@@ -70,6 +70,70 @@ __device__ __forceinline__ uint32_t pack4_i8(int32_t a, int32_t b, int32_t c, in
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)d << 24);
 }
 
+// Four int32 -> four int8 with saturation to [-128,127], a in the lowest byte.
+__device__ __forceinline__ uint32_t pack4_sat_i8(int32_t a, int32_t b, int32_t c, int32_t d) {
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(b), "r"(a), "r"(hi));
+    return w;
+}
+
+// Per-tensor (or per-channel) constants of the quantize fast path.
+struct QuantConsts {
+    float scale;
+    float rcp;          // correctly rounded 1/scale
+    int32_t zp;
+    bool fast;          // scale and 1/scale are normal numbers
+};
+__device__ __forceinline__ QuantConsts make_quant_consts(float scale, int32_t zp) {
+    QuantConsts c;
+    c.scale = scale;
+    c.zp = zp;
+    c.rcp = __frcp_rn(scale);
+    const float as = fabsf(scale), ar = fabsf(c.rcp);
+    c.fast = (as >= 1.17549435e-38f) && (as < INFINITY) && (ar >= 1.17549435e-38f) && (ar < INFINITY);
+    return c;
+}
+
+// (int32)roundf(x / scale) without a division or a float->int conversion per
+// element.  v = x * (1/scale) differs from the correctly rounded quotient
+// RN(x/scale) by less than |v| * 2^-22 (two roundings of 2^-24 each, with
+// margin), so roundf(v) == roundf(RN(x/scale)) whenever v is farther than that
+// from the nearest half-integer; `slow` is raised otherwise (and for NaN or
+// |v| >= 2^22) and the caller recomputes with the exact path.
+//   a = v + copysign(0.49999997, v)              roundf's argument (see round_half_away)
+//   y = RZ(a + copysign(2^23, v))                magnitude 2^23 + floor(|a|): truncation by an add
+//   f = y - copysign(2^23, v)                    = roundf(v), exact
+//   bits(f + 1.5*2^23) - 0x4B400000              = f as a two's-complement integer
+__device__ __forceinline__ int32_t quotient_round_fast(float x, float rcp, bool& slow) {
+    const float v = __fmul_rn(x, rcp);
+    const float a = __fadd_rn(v, copysignf(0.49999997f, v));
+    const float m = copysignf(8388608.0f, v);
+    const float f = __fsub_rn(__fadd_rz(a, m), m);
+    const float d = __fsub_rn(v, f);
+    const float e = __fmaf_rn(fabsf(v), 2.384185791015625e-07f, fabsf(d));     // |v| * 2^-22 + |d|
+    slow = slow || !(e < 0.5f);
+    return __float_as_int(__fadd_rn(f, 12582912.0f)) - 0x4B400000;
+}
+
+// Four elements at once: fast path, exact path for the whole quad when any
+// element needs it.  Same value as four quantize_one() calls, packed.
+__device__ __forceinline__ uint32_t quantize_quad_packed(float4 v, const QuantConsts& c) {
+    if (c.fast) {
+        bool slow = false;
+        const int32_t q0 = quotient_round_fast(v.x, c.rcp, slow);
+        const int32_t q1 = quotient_round_fast(v.y, c.rcp, slow);
+        const int32_t q2 = quotient_round_fast(v.z, c.rcp, slow);
+        const int32_t q3 = quotient_round_fast(v.w, c.rcp, slow);
+        // |q| < 2^22 here, so adding a zero point cannot wrap unless |zp| is
+        // within 2^22 of the int32 limits; that case takes the exact path.
+        if (!slow && ((uint32_t)c.zp + 0x40000000u) < 0x80000000u)
+            return pack4_sat_i8(q0 + c.zp, q1 + c.zp, q2 + c.zp, q3 + c.zp);
+    }
+    return pack4_i8(quantize_one(v.x, c.scale, c.zp), quantize_one(v.y, c.scale, c.zp),
+                    quantize_one(v.z, c.scale, c.zp), quantize_one(v.w, c.scale, c.zp));
+}
+
 __device__ __forceinline__ float warp_min(float v) {
     #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -8,7 +8,7 @@ namespace rplb {
 
 int gemm_tcgen05_status(bool clear);     // gemm_i8_tcgen05.cu
 
-static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05
+static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 single-CTA, 4 tcgen05 CTA pair
 
 // Below this many multiply-accumulates the persistent tensor-core kernel has
 // no advantage over the dp4a kernel (one tile is 128 x 256 outputs).
@@ -39,7 +39,7 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
 
     GemmProblem q = p;
     const bool big = p.M * p.N * (p.K ? p.K : 1) >= kTcMinMacs;
-    if (p.b_is_kn && (backend == 2 || big) && p.K % 16 == 0 && p.K && !(p.mode == EPI_REQUANT_I32 && (p.za || p.zb))) {
+    if (p.b_is_kn && (backend >= 2 || big) && p.K % 16 == 0 && p.K && !(p.mode == EPI_REQUANT_I32 && (p.za || p.zb))) {
         // Reorder B once into the K-contiguous layout the tensor-core kernel reads.
         const uint64_t gy = (p.K + 31) / 32;
         if (gy <= 65535) {
@@ -52,7 +52,7 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
             q.b_is_kn = 0;
         }
     }
-    if (backend == 2) return gemm_tcgen05(q, st);
+    if (backend >= 2) return gemm_tcgen05(q, st, backend - 2);
     if (big && gemm_tcgen05_supports(q)) return gemm_tcgen05(q, st);
     return gemm_simt(p, st);
 }
@@ -64,7 +64,7 @@ using namespace rplb;
 extern "C" {
 
 int rplb_gemm_backend(int which) {
-    if (which < 0 || which > 2) return g_backend.load();
+    if (which < 0 || which > 4) return g_backend.load();
     return g_backend.exchange(which);
 }
 

@@ -54,7 +54,8 @@ __device__ __forceinline__ float dequant_f32(int32_t acc, float a_scale, float w
 
 // Implemented in gemm_i8_simt.cu / gemm_i8_tcgen05.cu.
 int gemm_simt(const GemmProblem& p, cudaStream_t st);
-int gemm_tcgen05(const GemmProblem& p, cudaStream_t st);
+// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = a CTA pair (two SMs) per 256 x 256 tile.
+int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant = 0);
 // True when the tensor-core kernel can take the problem as it stands.
 bool gemm_tcgen05_supports(const GemmProblem& p);
 

@@ -82,15 +82,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Waits for the phase with the given parity.  Gives up after about a second
 // (or as soon as another role has given up) and returns false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, TcShared* sh, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0) {
-            if (sh->abort_flag) return false;
+            if (*abort_flag) return false;
             if (clock64() - t0 > 2000000000LL) {
-                sh->abort_flag = 1;
+                *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
             }
@@ -252,7 +252,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 uint32_t tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, tm, tn);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, sh, status, TC_WAIT_EMPTY)) { ok = false; break; }
+                    if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, &sh->abort_flag, status, TC_WAIT_EMPTY)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)stage * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_STAGE_BYTES;
                     mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
@@ -269,11 +269,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                if (!mbar_wait_bounded(&sh->acc_empty[acc], acc_phase ^ 1, sh, status, TC_WAIT_ACC_EMPTY)) break;
+                if (!mbar_wait_bounded(&sh->acc_empty[acc], acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * TILE_N;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait_bounded(&sh->full[stage], phase, sh, status, TC_WAIT_FULL)) { ok = false; break; }
+                    if (!mbar_wait_bounded(&sh->full[stage], phase, &sh->abort_flag, status, TC_WAIT_FULL)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
                     const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
@@ -315,7 +315,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 __syncwarp();
             }
-            bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, sh, status, TC_WAIT_ACC_FULL);
+            bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -346,6 +346,212 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------- the CTA-pair kernel
+// Two CTAs of a cluster (two SMs) work on one 256 x 256 output tile.  Each CTA
+// loads 128 rows of A and 128 rows of W per stage (32 KiB instead of 48), the
+// leader CTA's MMA thread issues tcgen05.mma.cta_group::2 (M = 256: the
+// instruction reads both CTAs' shared memory at the same offsets, so each W
+// half is fetched from shared memory once for both SMs), and each CTA's TMEM
+// receives its own 128 rows of the accumulator, drained by its own epilogue
+// warps.  Per SM this halves the W traffic through shared memory, which is what
+// bounds the single-CTA kernel.  No TMA multicast: each CTA loads its own halves.
+//
+// Barriers: full[] lives in the leader (both CTAs' TMA loads signal it; the
+// leader's producer arms it for the bytes of both); empty[] and acc_full[] are
+// signalled in both CTAs by a multicast tcgen05.commit; acc_empty[] lives in
+// the leader and collects the epilogue warps of both CTAs.
+constexpr int PAIR_TILE_M = 256;
+constexpr int kPairStages = 6;
+constexpr uint32_t PAIR_A_BYTES = 128 * TILE_K;           // 16 KiB: this CTA's 128 rows of A
+constexpr uint32_t PAIR_B_BYTES = 128 * TILE_K;           // 16 KiB: this CTA's 128 rows of W
+constexpr uint32_t PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+
+struct __align__(16) PairShared {
+    uint64_t full[kPairStages];
+    uint64_t empty[kPairStages];
+    uint64_t acc_full[kAccBuffers];
+    uint64_t acc_empty[kAccBuffers];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float w_scales[4 * TILE_N];
+    float bias[4 * TILE_N];
+};
+constexpr size_t PAIR_SMEM_BYTES = 1024 + (size_t)kPairStages * PAIR_STAGE_BYTES + sizeof(PairShared);
+
+constexpr uint32_t kIdescI8Pair = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(PAIR_TILE_M >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same variable in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion is counted on an mbarrier that may live in the
+// other CTA of the pair (bar_cluster_addr is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t c0, int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    PairShared* sh = reinterpret_cast<PairShared*>(smem + (size_t)kPairStages * PAIR_STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_cta_rank();             // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < kAccBuffers; a++) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 2 * (kEpilogueThreads / 32)); }
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // the peer's barriers are initialised too
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                uint32_t tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn);
+                const int32_t a_row = (int32_t)(tm * PAIR_TILE_M + cta * 128);
+                const int32_t w_row = (int32_t)(tn * TILE_N + cta * 128);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, &sh->abort_flag, status, TC_WAIT_EMPTY)) { ok = false; break; }
+                    uint8_t* a_dst = smem + (size_t)stage * PAIR_STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + PAIR_A_BYTES;
+                    const uint32_t leader_full = map_to_cta(smem_u32(&sh->full[stage]), 0);
+                    if (cta == 0) mbar_expect_tx(&sh->full[stage], 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(a_dst, &map_a, leader_full, (int32_t)(kb * TILE_K), a_row);
+                    tma_load_2d_pair(b_dst, &map_w, leader_full, (int32_t)(kb * TILE_K), w_row);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && cta == 0) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                if (!mbar_wait_bounded(&sh->acc_empty[acc], acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * TILE_N;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->full[stage], phase, &sh->abort_flag, status, TC_WAIT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * PAIR_STAGE_BYTES);
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + PAIR_A_BYTES);
+                    #pragma unroll
+                    for (int k = 0; k < TILE_K / MMA_K; k++) {
+                        tc_mma_i8_pair(d_tmem, a_desc + (uint64_t)(k * (MMA_K >> 4)), b_desc + (uint64_t)(k * (MMA_K >> 4)),
+                                       kIdescI8Pair, (kb | (uint32_t)k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair(&sh->empty[stage]);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit_pair(&sh->acc_full[acc]);
+                if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+        const uint32_t quarter = (uint32_t)warp & 3u;
+        const int ew = warp - kEpilogueWarp0;
+        float* s_scales = sh->w_scales + ew * TILE_N;
+        float* s_bias = sh->bias + ew * TILE_N;
+        const float a_scale = (MODE == EPI_DEQUANT_F32) ? __ldg(p.a_scale) : 0.0f;
+        uint32_t acc = 0, acc_phase = 0;
+        for (uint32_t tile = pair; tile < total_tiles; tile += num_pairs) {
+            uint32_t tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const uint64_t n0 = (uint64_t)tn * TILE_N;
+            const uint64_t m = (uint64_t)tm * PAIR_TILE_M + cta * 128 + quarter * 32 + lane;
+            if (MODE == EPI_DEQUANT_F32) {
+                __syncwarp();
+                for (int c = lane; c < TILE_N; c += 32) {
+                    const uint64_t n = n0 + c;
+                    s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
+                    s_bias[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
+                }
+                __syncwarp();
+            }
+            bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            #pragma unroll 1
+            for (int chunk = 0; chunk < TILE_N / 32; chunk++) {
+                const uint64_t n_first = n0 + (uint64_t)chunk * 32;
+                if (n_first >= p.N) break;
+                uint32_t r[32];
+                tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
+                tc_wait_ld();
+                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->acc_empty[acc]), 0));
+            if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ----------------------------------------------------------------- teardown
+    if (sh->abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither CTA leaves while the other may still touch its barriers or shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -434,7 +640,58 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmPro
     return launched("gemm_i8_tc_kernel");
 }
 
-int gemm_tcgen05(const GemmProblem& p, cudaStream_t st) {
+// How many CTA pairs can be resident at once (SMs pair up inside a TPC; a GPC
+// with an odd number of usable SMs leaves one without a partner).
+template <int MODE>
+static int max_resident_pairs(int* pairs) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (int rc = cuda_ok(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc_pair_kernel<MODE>, &cfg), "cudaOccupancyMaxActiveClusters")) return rc;
+    *pairs = n;
+    return 0;
+}
+
+template <int MODE>
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t num_kb,
+                          int* status_dev, cudaStream_t st) {
+    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)PAIR_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_pair_kernel)")) return rc;
+    int pairs = 0;
+    if (int rc = max_resident_pairs<MODE>(&pairs)) return rc;
+    if (pairs <= 0) return fail(RPLB_E_UNSUPPORTED, "no CTA pair fits on this device");
+    const uint32_t tiles_m = (uint32_t)((p.M + PAIR_TILE_M - 1) / PAIR_TILE_M);
+    const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
+    const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
+    if (tiles < (uint64_t)pairs) pairs = (int)tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned int)pairs);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_tc_pair_kernel<MODE>, ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    if (e != cudaSuccess) return cuda_ok(e, "cudaLaunchKernelEx(gemm_i8_tc_pair_kernel)");
+    return launched("gemm_i8_tc_pair_kernel");
+}
+
+// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = CTA pair per 256 x 256 tile.
+int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W, zero points 0");
     if (int prev = gemm_tcgen05_status(true))
@@ -444,15 +701,36 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st) {
     int* status_dev = nullptr;
     if (int rc = cuda_ok(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0), "cudaHostGetDevicePointer")) return rc;
 
+    const uint32_t num_kb = (uint32_t)((p.K + TILE_K - 1) / TILE_K);
+    unsigned int sms = (unsigned int)sm_count();
+    if (sms == 0) sms = 148;
+    if (variant == 0) {
+        // Measured on B200 (1000 W cap): un-throttled, the pair kernel keeps the
+        // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster;
+        // in a long run both sit at the power cap and the single-CTA kernel does
+        // ~6 % more work per joule.  So: the pair kernel for GEMMs short enough
+        // to finish before the power governor reacts, provided every pair of SMs
+        // gets a 256 x 256 tile of its own; the single-CTA kernel otherwise.
+        const uint64_t pair_tiles = ((p.M + PAIR_TILE_M - 1) / PAIR_TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
+        const double macs = (double)p.M * (double)p.N * (double)p.K;
+        variant = (pair_tiles >= sms / 2 && macs < 1.1e12) ? 2 : 1;
+    }
     CUtensorMap ma, mw;
+    if (variant == 2) {
+        if (int rc = make_map(&ma, p.A, p.M, p.K, 128)) return rc;
+        if (int rc = make_map(&mw, p.B, p.N, p.K, 128)) return rc;
+        switch (p.mode) {
+            case EPI_RAW_I32:     return launch_tc_pair<EPI_RAW_I32>(ma, mw, p, num_kb, status_dev, st);
+            case EPI_REQUANT_I32: return launch_tc_pair<EPI_REQUANT_I32>(ma, mw, p, num_kb, status_dev, st);
+            case EPI_DEQUANT_F32: return launch_tc_pair<EPI_DEQUANT_F32>(ma, mw, p, num_kb, status_dev, st);
+        }
+        return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
+    }
     if (int rc = make_map(&ma, p.A, p.M, p.K, TILE_M)) return rc;
     if (int rc = make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
     const uint32_t tiles_m = (uint32_t)((p.M + TILE_M - 1) / TILE_M);
     const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
-    const uint32_t num_kb = (uint32_t)((p.K + TILE_K - 1) / TILE_K);
     const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
-    unsigned int sms = (unsigned int)sm_count();
-    if (sms == 0) sms = 148;
     const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
     switch (p.mode) {
         case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);

@@ -123,10 +123,6 @@ minmax_kernel(const float* __restrict__ x, uint64_t n, uint64_t head, uint64_t n
 // ---------------------------------------------------------------------------
 // quantize  (src/rpl_core.c:521-527)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t quantize_quad(float4 v, float scale, int32_t zp) {
-    return pack4_i8(quantize_one(v.x, scale, zp), quantize_one(v.y, scale, zp),
-                    quantize_one(v.z, scale, zp), quantize_one(v.w, scale, zp));
-}
 
 // REVERSE walks the tensor from its end: after a forward min/max pass the end
 // of the tensor is what the L2 cache still holds.
@@ -135,8 +131,7 @@ __global__ void __launch_bounds__(kThreads)
 quantize_quads_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, uint64_t nquads,
                       float scale_imm, int32_t zp_imm,
                       const float* __restrict__ scale_dev, const int32_t* __restrict__ zp_dev) {
-    const float scale = scale_dev ? __ldg(scale_dev) : scale_imm;
-    const int32_t zp = zp_dev ? __ldg(zp_dev) : zp_imm;
+    const QuantConsts qc = make_quant_consts(scale_dev ? __ldg(scale_dev) : scale_imm, zp_dev ? __ldg(zp_dev) : zp_imm);
     // A CTA step covers kThreads*kUnroll consecutive quads; within it thread t
     // takes quads t, t+kThreads, ... so each warp instruction is contiguous.
     const uint64_t step = (uint64_t)kThreads * kUnroll;
@@ -152,7 +147,7 @@ quantize_quads_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, ui
         #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nquads) __stcs(q + i, quantize_quad(v[u], scale, zp));
+            if (i < nquads) __stcs(q + i, quantize_quad_packed(v[u], qc));
         }
     }
 }
@@ -258,11 +253,12 @@ per_channel_regs_kernel(const float* __restrict__ x, int8_t* __restrict__ q, flo
         }
         block_minmax(lo, hi, s_lo, s_hi);
         const float scale = channel_scale(lo, hi);
+        const QuantConsts qc = make_quant_consts(scale, 0);
         if (threadIdx.x == 0) { scales[c] = scale; if (zps) zps[c] = 0; }
         #pragma unroll
         for (int u = 0; u < QUADS; u++) {
             uint32_t i = threadIdx.x + u * kThreads;
-            if (i < row_quads) __stcs(out + i, quantize_quad(v[u], scale, 0));
+            if (i < row_quads) __stcs(out + i, quantize_quad_packed(v[u], qc));
         }
         __syncthreads();      // s_lo/s_hi are reused by the next channel
     }
@@ -294,6 +290,7 @@ per_channel_stream_kernel(const float* __restrict__ x, int8_t* __restrict__ q, f
         }
         block_minmax(lo, hi, s_lo, s_hi);
         const float scale = channel_scale(lo, hi);
+        const QuantConsts qc = make_quant_consts(scale, 0);
         if (threadIdx.x == 0) { scales[c] = scale; if (zps) zps[c] = 0; }
         if (vec) {
             const float4* r4 = reinterpret_cast<const float4*>(row);
@@ -303,7 +300,7 @@ per_channel_stream_kernel(const float* __restrict__ x, int8_t* __restrict__ q, f
             // is the most likely to be in cache still.
             for (uint64_t k = threadIdx.x; k < nq; k += kThreads) {
                 uint64_t i = nq - 1 - k;
-                __stcs(o4 + i, quantize_quad(__ldcs(r4 + i), scale, 0));
+                __stcs(o4 + i, quantize_quad_packed(__ldcs(r4 + i), qc));
             }
         } else {
             for (uint64_t i = threadIdx.x; i < channel_size; i += kThreads)
@@ -316,15 +313,35 @@ per_channel_stream_kernel(const float* __restrict__ x, int8_t* __restrict__ q, f
 // ---------------------------------------------------------------------------
 // dequantize  (src/ops_extended.c:67-70)
 // ---------------------------------------------------------------------------
+// (float)(q - zp) for |q - zp| < 2^22 without an int->float conversion:
+// 0x4B400000 is the bit pattern of 1.5 * 2^23, whose low mantissa bits count
+// in units of 1, so adding the integer to the pattern and subtracting
+// 1.5 * 2^23 as a float gives the integer's value exactly.
+__device__ __forceinline__ float int_to_float_small(int32_t i) {
+    return __fsub_rn(__int_as_float(0x4B400000 + i), 12582912.0f);
+}
+
+template <bool SMALL_ZP>
 __device__ __forceinline__ float4 dequant_quad(uint32_t w, float scale, int32_t zp) {
+    const int32_t q0 = (int32_t)(int8_t)(w & 0xff), q1 = (int32_t)(int8_t)((w >> 8) & 0xff);
+    const int32_t q2 = (int32_t)(int8_t)((w >> 16) & 0xff), q3 = (int32_t)(int8_t)(w >> 24);
     float4 r;
-    r.x = __fmul_rn((float)((int32_t)(int8_t)(w & 0xff) - zp), scale);
-    r.y = __fmul_rn((float)((int32_t)(int8_t)((w >> 8) & 0xff) - zp), scale);
-    r.z = __fmul_rn((float)((int32_t)(int8_t)((w >> 16) & 0xff) - zp), scale);
-    r.w = __fmul_rn((float)((int32_t)(int8_t)(w >> 24) - zp), scale);
+    if (SMALL_ZP) {
+        r.x = __fmul_rn(int_to_float_small(q0 - zp), scale);
+        r.y = __fmul_rn(int_to_float_small(q1 - zp), scale);
+        r.z = __fmul_rn(int_to_float_small(q2 - zp), scale);
+        r.w = __fmul_rn(int_to_float_small(q3 - zp), scale);
+    } else {
+        // int32 subtraction wraps, as the reference's compiled code does
+        r.x = __fmul_rn(__int2float_rn((int32_t)((uint32_t)q0 - (uint32_t)zp)), scale);
+        r.y = __fmul_rn(__int2float_rn((int32_t)((uint32_t)q1 - (uint32_t)zp)), scale);
+        r.z = __fmul_rn(__int2float_rn((int32_t)((uint32_t)q2 - (uint32_t)zp)), scale);
+        r.w = __fmul_rn(__int2float_rn((int32_t)((uint32_t)q3 - (uint32_t)zp)), scale);
+    }
     return r;
 }
 
+template <bool SMALL_ZP>
 __global__ void __launch_bounds__(kThreads)
 dequantize_quads_kernel(const uint32_t* __restrict__ q, float4* __restrict__ out, uint64_t nquads,
                         float scale, int32_t zp) {
@@ -341,7 +358,7 @@ dequantize_quads_kernel(const uint32_t* __restrict__ q, float4* __restrict__ out
         #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nquads) __stcs(out + i, dequant_quad(w[u], scale, zp));
+            if (i < nquads) __stcs(out + i, dequant_quad<SMALL_ZP>(w[u], scale, zp));
         }
     }
 }
@@ -364,7 +381,7 @@ dequantize_pc_quads_kernel(const uint32_t* __restrict__ q, const float* __restri
         #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nquads) __stcs(out + i, dequant_quad(__ldcs(q + i), __ldg(scales + i / row_quads), 0));
+            if (i < nquads) __stcs(out + i, dequant_quad<true>(__ldcs(q + i), __ldg(scales + i / row_quads), 0));
         }
     }
 }
@@ -452,7 +469,10 @@ int rplb_dequantize_i8_f32(const int8_t* q, float* out, uint64_t n, float scale,
     uint64_t nquads = vec ? n / 4 : 0;
     if (nquads) {
         unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
-        dequantize_quads_kernel<<<grid, kThreads, 0, st>>>((const uint32_t*)q, (float4*)out, nquads, scale, zero_point);
+        if (zero_point > -(1 << 21) && zero_point < (1 << 21))
+            dequantize_quads_kernel<true><<<grid, kThreads, 0, st>>>((const uint32_t*)q, (float4*)out, nquads, scale, zero_point);
+        else
+            dequantize_quads_kernel<false><<<grid, kThreads, 0, st>>>((const uint32_t*)q, (float4*)out, nquads, scale, zero_point);
         if (int rc = launched("dequantize_quads_kernel")) return rc;
     }
     if (nquads * 4 < n) {

@@ -74,9 +74,11 @@ class ShardedQuantizedLinear:
     src/rpl_nn.c:55-77) on the INT8 path of ``linear_int8``.
     """
 
-    def __init__(self, wq, w_scales, bias=None, n_total=None, rank=0, world=1, relu=False):
+    def __init__(self, wq, w_scales, bias=None, n_total=None, rank=0, world=1, relu=False, group=None,
+                 shard_reduction=True):
         self.wq, self.w_scales, self.bias = wq, w_scales, bias
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.group = rank, world, group
+        self.shard_reduction = shard_reduction
         self.n_total = int(n_total if n_total is not None else wq.shape[0])
         self.relu = relu
         self._xq = None
@@ -91,33 +93,61 @@ class ShardedQuantizedLinear:
         wq, scales, _ = D.quantize_per_channel(w_shard)
         return cls(wq, scales, bias, **kw)
 
-    def forward(self, x, out=None, row_chunks=None, after_chunk=None):
-        """x: fp32 CUDA [M,K].  Returns the fp32 column block [M, count].
+    def quantize_activation(self, x):
+        """Per-tensor symmetric quantization of the fp32 activation ``[M,K]``.
 
-        ``row_chunks`` splits the GEMM into that many row blocks (same results);
-        ``after_chunk(i, r0, r1)`` is called after block i has been launched.
+        Returns ``(xq, a_scale)``: the int8 activation and its scale as a
+        one-element device tensor.  With more than one rank (every rank holds the
+        whole activation) the min/max pass is split by rows: each rank reduces its
+        row block, one scalar max-all-reduce makes the result global, and the
+        quantize pass runs locally with that scale.
         """
         from . import device as D
         M, K = x.shape
         if self._xq is None or self._xq.shape != x.shape or self._xq.device != x.device:
             self._xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
             self._params = torch.empty(8, dtype=torch.float32, device=x.device)
-        D.quantize_symmetric(x, out=self._xq, params=self._params)
         a_scale = self._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+        if self.world > 1 and self.shard_reduction and dist.is_initialized():
+            r0, rc = shard_range(M, self.world, self.rank, 1)
+            local = D.minmax(x[r0:r0 + rc])
+            pair = torch.stack((-local[D.QPARAM_MIN], local[D.QPARAM_MAX]))
+            dist.all_reduce(pair, op=dist.ReduceOp.MAX, group=self.group)
+            # fmaxf(|min|, |max|) / 127.0f, the reference's statement, in fp32 on the device
+            a_scale.copy_((torch.maximum(pair[0].abs(), pair[1].abs()) / 127.0).reshape(1))
+            D.quantize_dev(x, a_scale, out=self._xq)
+        else:
+            D.quantize_symmetric(x, out=self._xq, params=self._params)
+        return self._xq, a_scale
+
+    def gemm(self, xq, a_scale, out=None, row_chunks=None, after_chunk=None):
+        """INT8 GEMM of the quantized activation against this rank's weight rows,
+        fused fp32 epilogue; returns the column block ``[M, count]``.
+
+        ``row_chunks`` splits the GEMM into that many row blocks (same results);
+        ``after_chunk(i, r0, r1)`` is called after block i has been launched.
+        """
+        from . import device as D
+        M = xq.shape[0]
         count = self.wq.shape[0]
         if out is None:
-            out = torch.empty((M, count), dtype=torch.float32, device=x.device)
+            out = torch.empty((M, count), dtype=torch.float32, device=xq.device)
         if not row_chunks or row_chunks <= 1:
-            D.linear_i8_dequant(self._xq, self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out)
+            D.linear_i8_dequant(xq, self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out)
             return out
         step = (M + row_chunks - 1) // row_chunks
         step = (step + 127) // 128 * 128
         for i, r0 in enumerate(range(0, M, step)):
             r1 = min(M, r0 + step)
-            D.linear_i8_dequant(self._xq[r0:r1], self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out[r0:r1])
+            D.linear_i8_dequant(xq[r0:r1], self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out[r0:r1])
             if after_chunk is not None:
                 after_chunk(i, r0, r1)
         return out
+
+    def forward(self, x, out=None, row_chunks=None, after_chunk=None):
+        """x: fp32 CUDA [M,K] -> fp32 column block [M, count] (quantize, then GEMM)."""
+        xq, a_scale = self.quantize_activation(x)
+        return self.gemm(xq, a_scale, out=out, row_chunks=row_chunks, after_chunk=after_chunk)
 
     def forward_host(self, x_host, out_host, row_chunks=8):
         """Host buffers in, host buffers out (page-locked for full PCIe speed).

@@ -9,7 +9,7 @@ from conftest import bits
 
 pytestmark = pytest.mark.gpu
 
-SIMT, TC = 1, 2
+SIMT, TC, TC_SINGLE, TC_PAIR = 1, 2, 3, 4      # rplb_gemm_backend codes
 
 
 def same(a, b):
@@ -70,22 +70,23 @@ def test_tcgen05_raw_and_bias(cuda, lib, port, backend, mnk):
     W = rng.integers(-128, 128, (N, K), dtype=np.int8)
     b = rng.integers(-128, 128, N, dtype=np.int8)
     want = port.linear(A, W)
-    D.gemm_backend(TC)
-    got = host(D.linear_i8(dev(A, cuda), dev(W, cuda)))
-    torch.cuda.synchronize()
-    assert D.kernel_status(True) == 0
-    assert same(got, want)
-    assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda), dev(b, cuda))), port.linear(A, W, b))
+    for which in (TC_SINGLE, TC_PAIR, TC):
+        D.gemm_backend(which)
+        got = host(D.linear_i8(dev(A, cuda), dev(W, cuda)))
+        torch.cuda.synchronize()
+        assert D.kernel_status(True) == 0
+        assert same(got, want), which
+        assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda), dev(b, cuda))), port.linear(A, W, b)), which
     D.gemm_backend(SIMT)
     assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), want)
 
 
 @pytest.mark.parametrize("mnk", [(64, 64, 64), (130, 300, 784), (512, 512, 512), (33, 77, 19), (5, 3, 1)])
-@pytest.mark.parametrize("which", [SIMT, TC])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
 def test_requant_epilogue(cuda, lib, port, backend, mnk, which):
     D = backend
     M, N, K = mnk
-    if which == TC and K % 16:
+    if which != SIMT and K % 16:
         pytest.skip("tensor-core kernel needs K % 16 == 0")
     rng = np.random.default_rng(M + N + K)
     A = rng.integers(-128, 128, (M, K), dtype=np.int8)
@@ -99,7 +100,7 @@ def test_requant_epilogue(cuda, lib, port, backend, mnk, which):
 
 
 @pytest.mark.parametrize("mnk", [(128, 256, 128), (37, 23, 144), (130, 300, 784), (256, 10, 128), (512, 512, 512)])
-@pytest.mark.parametrize("which", [SIMT, TC])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
 @pytest.mark.parametrize("relu", [False, True])
 def test_fused_dequant_epilogue(cuda, lib, port, backend, mnk, which, relu):
     D = backend
@@ -130,7 +131,7 @@ def test_fused_epilogue_writes_a_column_block_in_place(cuda, lib, port, backend)
     ws = ((rng.random(N) + 0.5) * 1e-4).astype(np.float32)
     want = port.linear_dequant(A, W, 0.01, ws, None, False)
     a_dev = dev(np.array([0.01], np.float32), cuda)
-    for which in (SIMT, TC):
+    for which in (SIMT, TC_SINGLE, TC_PAIR):
         D.gemm_backend(which)
         full = torch.full((M, NT), -7.0, device=cuda)
         D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda), out=full[:, 256:512])
@@ -150,7 +151,7 @@ def test_config1_512_cubed_end_to_end(cuda, lib, port, backend):
     wqa, sa = port.quantize_symmetric(A)
     wqb, sb = port.quantize_symmetric(Bt)
     assert same(host(qa), wqa) and same(host(qb), wqb)
-    for which in (SIMT, TC):
+    for which in (SIMT, TC_SINGLE, TC_PAIR):
         D.gemm_backend(which)
         assert same(host(D.linear_i8(qa, qb)), port.linear(wqa, wqb))
         Bkn = np.ascontiguousarray(wqb.T)
@@ -169,8 +170,10 @@ def test_tcgen05_matches_dp4a_at_projection_size(cuda, lib, backend):
     g.manual_seed(3)
     A = torch.randint(-128, 128, (4096, 4096), device=cuda, generator=g, dtype=torch.int8)
     W = torch.randint(-128, 128, (4096, 4096), device=cuda, generator=g, dtype=torch.int8)
-    D.gemm_backend(TC)
+    D.gemm_backend(TC_PAIR)
     c_tc = D.linear_i8(A, W)
+    D.gemm_backend(TC_SINGLE)
+    assert torch.equal(D.linear_i8(A, W), c_tc)
     D.gemm_backend(SIMT)
     c_simt = D.linear_i8(A, W)
     assert torch.equal(c_tc, c_simt)

@@ -154,3 +154,31 @@ def test_sampled_parity_at_sweep_size(cuda, lib, port):
         s = int(start)
         hx = host(x[s:s + 4096])
         assert same(host(q[s:s + 4096]), port.quantize(hx, scale, 0))
+
+
+def test_near_tie_inputs_and_extreme_parameters(cuda, lib, port):
+    """Inputs a few ulps either side of (k + 0.5) * scale and k * scale, where a
+    reciprocal multiply and a true division can round differently; scales and
+    zero points outside the fast path's range."""
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(99)
+    for scale in (np.float32(0.39370078), np.float32(1.0 / 3.0), np.float32(2.3622048), np.float32(1e-3),
+                  np.float32(7.0), np.float32(50.0) / np.float32(127.0)):
+        k = rng.integers(-150, 150, 200_000)
+        half = (k + 0.5).astype(np.float32) * scale
+        whole = k.astype(np.float32) * scale
+        x = np.concatenate([half, whole])
+        ulps = rng.integers(-4, 5, x.size)
+        x = (x.view(np.int32) + ulps).view(np.float32)
+        xd = dev(x, cuda)
+        for zp in (0, 3, -128, 1000):
+            assert same(host(D.quantize(xd, float(scale), zp)), port.quantize(x, scale, zp))
+    x = sweep_tensor(rng, (100_003,))
+    xd = dev(x, cuda)
+    for scale, zp in ((1e-41, 0), (3e38, 0), (1e-30, 5), (0.05, 2**31 - 1), (0.05, -2**31), (0.05, 2**30 + 7),
+                      (float("inf"), 0), (0.0, 0), (-0.25, 4), (float("nan"), 0)):
+        assert same(host(D.quantize(xd, scale, zp)), port.quantize(x, scale, zp)), (scale, zp)
+    q = rng.integers(-128, 128, 100_003, dtype=np.int8)
+    qd = dev(q, cuda)
+    for scale, zp in ((0.1, 2**21 - 1), (0.1, -(2**21) + 1), (0.1, 2**21), (0.1, -(2**22)), (0.1, 2**31 - 1), (0.1, -2**31), (3e38, 7)):
+        assert same(host(D.dequantize(qd, scale, zp)), port.dequantize(q, scale, zp)), (scale, zp)
