@@ -237,15 +237,19 @@ def quantize_sweep(torch, D, dev, peaks):
     for name, bytes_per_elem, fn in cases:
         for _ in range(3):
             fn()
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        # 20 launches between one pair of events (a kernel here lasts ~50 us: an event
+        # pair around every launch would time the launch gap as well), 5 such groups.
+        reps, groups = 20, 5
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)]
         before = D.launch_count()
         for a, b in evs:
             a.record()
-            fn()
+            for _ in range(reps):
+                fn()
             b.record()
         torch.cuda.synchronize()
         launches += D.launch_count() - before
-        ms = sorted(event_ms(evs))
+        ms = sorted(t / reps for t in event_ms(evs))
         med = ms[len(ms) // 2]
         gbs = bytes_per_elem * n / (med * 1e-3) / 1e9
         res[name] = {"ms": med, "gbs": gbs, "bytes_per_elem": bytes_per_elem, "frac": gbs / peaks["hbm_gbs"]}
@@ -388,6 +392,9 @@ def run_ours(a):
             dist.destroy_process_group()
         return
 
+    # DRAM traffic of the GEMM from the ncu capture at 16384 x 16384 x 8192
+    # (profiles/gemm_i8_tc_kernel_8192cubed.md): 8.39 B per output element at K = 8192.
+    traffic = 8.39 * M * count if K == 8192 else None
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
     line = {
@@ -399,7 +406,8 @@ def run_ours(a):
                    % (M * K * 4 / 2**30, M * count * 4 / 2**30)},
         "breakdown_ms": {"quantize_A": quant_ms, "gemm_with_epilogue": gemm_ms},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                     "frac": achieved / int8_peak, "traffic": None, "kernel": "gemm_i8_tc_kernel",
+                     "frac": achieved / int8_peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by output elements)",
+                     "algorithmic_bytes": float(M * K + count * K + 4 * M * count), "kernel": "gemm_i8_tc_kernel",
                      "peak_note": "2 x bf16_tflops_sustained of %s (int8 dense = 2 x bf16 dense)" % peaks["source"],
                      "frac_of_nominal_4500": achieved / 4500.0},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,

@@ -98,22 +98,22 @@ __device__ __forceinline__ QuantConsts make_quant_consts(float scale, int32_t zp
 // (int32)roundf(x / scale) without a division or a float->int conversion per
 // element.  v = x * (1/scale) differs from the correctly rounded quotient
 // RN(x/scale) by less than |v| * 2^-22 (two roundings of 2^-24 each, with
-// margin), so roundf(v) == roundf(RN(x/scale)) whenever v is farther than that
+// margin), so both round to the same integer whenever v is farther than that
 // from the nearest half-integer; `slow` is raised otherwise (and for NaN or
 // |v| >= 2^22) and the caller recomputes with the exact path.
-//   a = v + copysign(0.49999997, v)              roundf's argument (see round_half_away)
-//   y = RZ(a + copysign(2^23, v))                magnitude 2^23 + floor(|a|): truncation by an add
-//   f = y - copysign(2^23, v)                    = roundf(v), exact
-//   bits(f + 1.5*2^23) - 0x4B400000              = f as a two's-complement integer
+//   t = v + 1.5*2^23          the add rounds v to the nearest integer (ties to even)
+//   bits(t) - 0x4B400000      that integer, two's complement
+//   f = t - 1.5*2^23          the same integer as a float, exact
+//   d = v - f                 in [-0.5, 0.5]; |d| = 0.5 exactly at a tie
+// Away from ties, nearest-even and roundf's ties-away agree; ties are sent to
+// the exact path by the same test that guards the reciprocal.
 __device__ __forceinline__ int32_t quotient_round_fast(float x, float rcp, bool& slow) {
     const float v = __fmul_rn(x, rcp);
-    const float a = __fadd_rn(v, copysignf(0.49999997f, v));
-    const float m = copysignf(8388608.0f, v);
-    const float f = __fsub_rn(__fadd_rz(a, m), m);
-    const float d = __fsub_rn(v, f);
+    const float t = __fadd_rn(v, 12582912.0f);
+    const float d = __fsub_rn(v, __fsub_rn(t, 12582912.0f));
     const float e = __fmaf_rn(fabsf(v), 2.384185791015625e-07f, fabsf(d));     // |v| * 2^-22 + |d|
     slow = slow || !(e < 0.5f);
-    return __float_as_int(__fadd_rn(f, 12582912.0f)) - 0x4B400000;
+    return __float_as_int(t) - 0x4B400000;
 }
 
 // Four elements at once: fast path, exact path for the whole quad when any
