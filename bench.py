@@ -283,7 +283,9 @@ def run_ours(a):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # A short timeout: a rank that falls out of step fails in minutes, not in ten.
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     peaks = measured_peaks()
     M, N, K = a.m, a.n, a.k
     D.gemm_backend(a.gemm_backend)
@@ -331,10 +333,17 @@ def run_ours(a):
     # until it has, then open the timed region.
     if not a.no_clocks:
         sampler.start()
+        # Every rank must run the same number of pre-roll steps (a step contains a
+        # collective when N > 1): rank 0 sizes it for about a second and tells the others.
         t_pre = time.time()
-        while time.time() - t_pre < 1.0:
+        layer.forward(A, out=out)
+        torch.cuda.synchronize()
+        n_pre = torch.tensor([max(1, min(2000, int(1.0 / max(time.time() - t_pre, 1e-4))))], device=dev)
+        if world > 1:
+            dist.broadcast(n_pre, src=0)
+        for _ in range(int(n_pre.item())):
             layer.forward(A, out=out)
-            torch.cuda.synchronize()
+        torch.cuda.synchronize()
     barrier()
     sampler.t_begin = time.time()
     launches0 = D.launch_count()
@@ -361,6 +370,14 @@ def run_ours(a):
     ms_max = float(t.item())
     gemm_ms = sum(event_ms(gemm_ev)) / a.steps
     quant_ms = sum(event_ms(quant_ev)) / a.steps
+    per_rank = torch.tensor([gemm_ms, quant_ms, ms], device=dev)
+    if world > 1:
+        gathered = [torch.empty_like(per_rank) for _ in range(world)]
+        dist.all_gather(gathered, per_rank)
+        per_rank = torch.stack(gathered)
+    else:
+        per_rank = per_rank.reshape(1, 3)
+    per_rank = [[round(float(v), 4) for v in row] for row in per_rank.cpu()]
 
     # ---- end to end through host buffers ----
     e2e = None
@@ -404,7 +421,8 @@ def run_ours(a):
         "config": {"workload": workload_name(a), "parallelism": "N-split over %d rank(s), output left column-sharded" % world,
                    "columns_per_rank": count, "l2": "no flush: per-step inputs and outputs exceed L2 (A %.1f GiB fp32, out %.1f GiB per rank)"
                    % (M * K * 4 / 2**30, M * count * 4 / 2**30)},
-        "breakdown_ms": {"quantize_A": quant_ms, "gemm_with_epilogue": gemm_ms},
+        "breakdown_ms": {"quantize_A": quant_ms, "gemm_with_epilogue": gemm_ms,
+                         "per_rank_gemm_quant_step": per_rank},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by output elements)",
                      "algorithmic_bytes": float(M * K + count * K + 4 * M * count), "kernel": "gemm_i8_tc_kernel",
@@ -431,6 +449,9 @@ def run_ours(a):
 def main():
     a = parse_args()
     if a.impl == "reference":
+        # torchrun pins OMP_NUM_THREADS to 1; the CPU arm is meant to use every host
+        # core, and the OpenMP runtime reads the variable when it is first loaded.
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         run_reference_arm(a)
     else:
         run_ours(a)
