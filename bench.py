@@ -36,6 +36,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c5"],
+                    help="c5 = large sharded GEMM (the benchmark); c1 512^3, c2 quantized MLP, c3 transformer "
+                         "projections: secondary single-GPU lines, device-resident timing only")
     ap.add_argument("--m", type=int, default=65536)
     ap.add_argument("--n", type=int, default=65536)
     ap.add_argument("--k", type=int, default=8192)
@@ -446,8 +449,100 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def run_secondary(a):
+    """Secondary configurations on one GPU: device-resident timing, same metric."""
+    import torch
+
+    from rpl_b200 import device as D
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = measured_peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED0000 + int(a.workload[1]) * 16)
+    one = lambda p: p[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+    if a.workload == "c1":
+        name = "INT8 GEMM 512x512x512: A, B fp32 N(0,1), both per-tensor symmetric, fp32 out acc*sA*sB"
+        A = torch.randn((512, 512), device=dev, generator=g)
+        Bt = torch.randn((512, 512), device=dev, generator=g)          # stored [N,K]
+        bq, pb = D.quantize_symmetric(Bt)
+        ws = pb[D.QPARAM_SCALE_SYM].repeat(512).contiguous()
+        out = torch.empty((512, 512), device=dev)
+        aq, pa = torch.empty((512, 512), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
+        ops, hbm_bytes = 2.0 * 512 ** 3, None
+
+        def step():
+            D.quantize_symmetric(A, out=aq, params=pa)
+            D.linear_i8_dequant(aq, bq, one(pa), ws, out=out)
+        note = "launch-latency bound: 0.27 GOP is ~0.1 us of tensor work"
+    elif a.workload == "c2":
+        name = "quantized MLP 784->128->10, batch 65536: X U[0,1) per tensor, W N(0,0.05) per channel, ReLU, fp32 logits"
+        Bn = 65536
+        X = torch.rand((Bn, 784), device=dev, generator=g)
+        w1q, w1s, _ = D.quantize_per_channel(torch.randn((128, 784), device=dev, generator=g) * 0.05)
+        w2q, w2s, _ = D.quantize_per_channel(torch.randn((10, 128), device=dev, generator=g) * 0.05)
+        b1 = torch.randn(128, device=dev, generator=g) * 0.05
+        b2 = torch.randn(10, device=dev, generator=g) * 0.05
+        xq, px = torch.empty((Bn, 784), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
+        h, hq, ph = torch.empty((Bn, 128), device=dev), torch.empty((Bn, 128), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
+        logits = torch.empty((Bn, 10), device=dev)
+        ops = 2.0 * Bn * (784 * 128 + 128 * 10)
+        # X read twice (min/max, quantize) + int8 X written and read + hidden fp32/int8 + logits
+        hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4 + 4 + 1 + 1) + 10 * 4)
+
+        def step():
+            D.quantize_symmetric(X, out=xq, params=px)
+            D.linear_i8_dequant(xq, w1q, one(px), w1s, b1, relu=True, out=h)
+            D.quantize_symmetric(h, out=hq, params=ph)
+            D.linear_i8_dequant(hq, w2q, one(ph), w2s, b2, relu=False, out=logits)
+        note = "HBM-bound: 13.3 GOP over ~0.7 GB of traffic"
+    else:
+        name = "transformer projections: tokens 32768 x d_model 4096, Q/K/V/O weights 4096x4096 per channel, bias, fp32 out"
+        T, Dm = 32768, 4096
+        X = torch.randn((T, Dm), device=dev, generator=g)
+        ws_ = [D.quantize_per_channel(torch.randn((Dm, Dm), device=dev, generator=g) * 0.02) for _ in range(4)]
+        bs = [torch.randn(Dm, device=dev, generator=g) * 0.02 for _ in range(4)]
+        outs = [torch.empty((T, Dm), device=dev) for _ in range(4)]
+        xq, px = torch.empty((T, Dm), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
+        ops, hbm_bytes = 4 * 2.0 * T * Dm * Dm, None
+
+        def step():
+            D.quantize_symmetric(X, out=xq, params=px)
+            for (wq, wsc, _), b, o in zip(ws_, bs, outs):
+                D.linear_i8_dequant(xq, wq, one(px), wsc, b, out=o)
+        note = "X quantized once per step, four GEMMs with fused per-channel dequant + bias"
+    for _ in range(max(a.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = D.launch_count()
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if D.kernel_status(True) != 0:
+        raise RuntimeError("the tcgen05 kernel reported an expired wait")
+    ms = e0.elapsed_time(e1) / a.steps
+    line = {"metric": METRIC, "value": ops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1, "steps": a.steps,
+            "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": {"workload": name, "note": note},
+            "gpu_launches": int(D.launch_count() - l0)}
+    if hbm_bytes:
+        gbs = hbm_bytes / (ms * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": gbs / peaks["hbm_gbs"], "traffic": None}
+    else:
+        t = ops / (ms * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "achieved": t, "peak": 2.0 * peaks["bf16_sustained"], "unit": "TOP/s",
+                            "frac": t / (2.0 * peaks["bf16_sustained"]), "traffic": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     a = parse_args()
+    if a.impl != "reference" and a.workload != "c5":
+        run_secondary(a)
+        return
     if a.impl == "reference":
         # torchrun pins OMP_NUM_THREADS to 1; the CPU arm is meant to use every host
         # core, and the OpenMP runtime reads the variable when it is first loaded.

@@ -1,0 +1,112 @@
+"""The benchmark configurations as parity cases: the quantized MLP
+(784 -> 128 -> 10, batch 65536), one transformer projection (32768 x 4096 x 4096)
+and a slab of the large sharded GEMM (K = 8192), against the CPU checker."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits
+
+pytestmark = pytest.mark.gpu
+
+
+def same(a, b):
+    return np.array_equal(bits(np.asarray(a)), bits(np.asarray(b)))
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def test_quantized_mlp_784_128_10_batch_65536(cuda, lib, port):
+    """X ~ U[0,1) per tensor, weights ~ N(0,0.05) per output channel, ReLU between
+    the layers, fp32 logits: every intermediate tensor bit for bit."""
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(0x5EED0020)
+    B = 65536
+    X = rng.random((B, 784), dtype=np.float32)
+    W1 = (rng.standard_normal((128, 784)) * 0.05).astype(np.float32)
+    W2 = (rng.standard_normal((10, 128)) * 0.05).astype(np.float32)
+    b1 = (rng.standard_normal(128) * 0.05).astype(np.float32)
+    b2 = (rng.standard_normal(10) * 0.05).astype(np.float32)
+    d = lambda a: torch.from_numpy(a).to(cuda)
+
+    w1q, w1s, _ = D.quantize_per_channel(d(W1))
+    w2q, w2s, _ = D.quantize_per_channel(d(W2))
+    xq, px = D.quantize_symmetric(d(X))
+    h = D.linear_i8_dequant(xq, w1q, px[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], w1s, d(b1), relu=True)
+    hq, ph = D.quantize_symmetric(h)
+    logits = D.linear_i8_dequant(hq, w2q, ph[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], w2s, d(b2), relu=False)
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
+
+    cw1q, cw1s, _ = port.quantize_per_channel(W1, 128)
+    cw2q, cw2s, _ = port.quantize_per_channel(W2, 10)
+    cxq, cxs = port.quantize_symmetric(X)
+    assert same(host(w1q), cw1q) and same(host(w1s), cw1s) and same(host(w2q), cw2q) and same(host(w2s), cw2s)
+    assert same(host(xq), cxq) and same(host(px)[D.QPARAM_SCALE_SYM], cxs)
+    ch = port.linear_dequant(cxq, cw1q, cxs, cw1s, b1, relu=True)
+    assert same(host(h), ch)
+    chq, chs = port.quantize_symmetric(ch)
+    assert same(host(hq), chq) and same(host(ph)[D.QPARAM_SCALE_SYM], chs)
+    cl = port.linear_dequant(chq, cw2q, chs, cw2s, b2, relu=False)
+    got = host(logits)
+    assert np.allclose(got, cl, rtol=1e-5, atol=0) and same(got, cl)
+
+
+def test_transformer_projection_32768x4096x4096(cuda, lib, port):
+    """One of the four projections at full size: sampled tiles against the checker,
+    and the fused fp32 epilogue against the raw accumulators of the dp4a kernel."""
+    from rpl_b200 import device as D
+    g = torch.Generator(device=cuda)
+    g.manual_seed(0x5EED0030)
+    T, Dm = 32768, 4096
+    X = torch.randn((T, Dm), device=cuda, generator=g)
+    W = torch.randn((Dm, Dm), device=cuda, generator=g) * 0.02
+    bias = torch.randn(Dm, device=cuda, generator=g) * 0.02
+    xq, px = D.quantize_symmetric(X)
+    wq, ws, _ = D.quantize_per_channel(W)
+    a_scale = px[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+    prev = D.gemm_backend(0)
+    try:
+        out = D.linear_i8_dequant(xq, wq, a_scale, ws, bias)
+        D.gemm_backend(1)
+        acc = D.linear_i8(xq[:2048], wq)                       # dp4a kernel, raw int32
+    finally:
+        D.gemm_backend(prev)
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
+    # epilogue arithmetic in torch fp32, one rounding per step (no fused multiply-add in these ops)
+    want = (acc.to(torch.float32) * a_scale) * ws[None, :]
+    want = want + bias[None, :]
+    assert torch.equal(out[:2048], want)
+    rng = np.random.default_rng(2)
+    hs, hws, hb = float(host(a_scale)[0]), host(ws), host(bias)
+    for _ in range(6):
+        m0, n0 = int(rng.integers(0, T - 128)), int(rng.integers(0, Dm - 128))
+        hx, hw = host(xq[m0:m0 + 128]), host(wq[n0:n0 + 128])
+        assert same(hx, port.quantize(host(X[m0:m0 + 128]), hs, 0))
+        ref = port.linear_dequant(hx, hw, hs, hws[n0:n0 + 128], hb[n0:n0 + 128])
+        assert same(host(out[m0:m0 + 128, n0:n0 + 128]), ref)
+
+
+def test_large_sharded_gemm_slab(cuda, lib, port):
+    """K = 8192, weight rows split over 8 'ranks' of 2048 columns each (run one after
+    the other on this GPU), 256 rows of A: the assembled output equals the checker's."""
+    from rpl_b200 import device as D
+    from rpl_b200.sharded import ShardedQuantizedLinear, shard_range
+    g = torch.Generator(device=cuda)
+    g.manual_seed(0x5EED0050)
+    M, K, N, world = 256, 8192, 16384, 8
+    A = torch.randn((M, K), device=cuda, generator=g)
+    W = torch.randn((N, K), device=cuda, generator=g) * 0.02
+    full = torch.empty((M, N), device=cuda)
+    for r in range(world):
+        b, c = shard_range(N, world, r, 256)
+        layer = ShardedQuantizedLinear.from_fp32(W[b:b + c].contiguous(), n_total=N, rank=r, world=1)
+        layer.forward(A, out=full[:, b:b + c])
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
+    hq, hs = port.quantize_symmetric(host(A))
+    hwq, hws, _ = port.quantize_per_channel(host(W), N)
+    assert same(host(full), port.linear_dequant(hq, hwq, hs, hws))
