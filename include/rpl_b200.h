@@ -233,6 +233,28 @@ int  rplb_linear_i8_dequant_f32(const int8_t* x, const int8_t* w, float* out,
                                 const float* a_scale, const float* w_scales, const float* bias,
                                 int relu, void* stream);
 
+/* The same call that also reports what the next layer's per-tensor quantizer
+ * needs, so that layer can skip its min/max pass over the fp32 output (no
+ * counterpart in the reference, which always re-scans: src/rpl_quantization.c:79-85).
+ * absmax (device, one float) receives max |out| over non-NaN outputs; if
+ * next_scale (device, one float) is not NULL it receives absmax / 127.0f, the
+ * scale tensor_quantize_int8_symmetric would compute for `out`
+ * (src/rpl_quantization.c:87-88).  Feed it to rplb_quantize_f32_i8_dev. */
+int  rplb_linear_i8_dequant_f32_absmax(const int8_t* x, const int8_t* w, float* out,
+                                       uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                                       const float* a_scale, const float* w_scales, const float* bias,
+                                       int relu, float* absmax, float* next_scale, void* stream);
+
+/* Chained quantized layers with a calibrated (static) output scale: the fp32
+ * value of rplb_linear_i8_dequant_f32 is quantized in the epilogue exactly as
+ * tensor_quantize_int8 would (src/rpl_core.c:523-526) and stored as int8, so
+ * the fp32 activation never reaches memory.  out_scale: one float on the
+ * device (e.g. from calibrator_compute_params, src/rpl_quantization.c:55-67). */
+int  rplb_linear_i8_requant_i8(const int8_t* x, const int8_t* w, int8_t* out,
+                               uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                               const float* a_scale, const float* w_scales, const float* bias,
+                               int relu, const float* out_scale, int32_t out_zero_point, void* stream);
+
 /* tensor_relu_inplace, scalar branch (src/rpl_core.c:254-255): x < 0 -> 0 in
  * place.  (The fused entry point above applies it inside the GEMM epilogue.) */
 int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);

@@ -102,6 +102,8 @@ SIGNATURES = {
     "rplb_linear_i8_i32": ("rc", [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "rplb_gemm_i8_requant_i32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _f, _f, _f, _i, _i, _vp]),
     "rplb_linear_i8_dequant_f32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp]),
+    "rplb_linear_i8_dequant_f32_absmax": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
+    "rplb_linear_i8_requant_i8": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _i, _vp]),
     "rplb_gemm_backend": (C.c_int, [C.c_int]),
     "rplb_kernel_status": (C.c_int, [C.c_int]),
     "rplb_shard_range": ("rc", [_u64, C.c_int, C.c_int, _u64, C.POINTER(_u64), C.POINTER(_u64)]),

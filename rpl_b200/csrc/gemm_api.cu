@@ -29,6 +29,42 @@ __global__ void transpose_i8_kernel(const int8_t* __restrict__ B, int8_t* __rest
     }
 }
 
+// sums[r] = sum_k X[r,k] of a row-major [rows, K] int8 matrix: one warp per row,
+// 16-byte loads when the row allows it, dp4a against a word of ones.
+__global__ void row_sums_i8_kernel(const int8_t* __restrict__ X, int32_t* __restrict__ sums, uint64_t rows, uint64_t K) {
+    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int8_t* x = X + row * K;
+    int32_t acc = 0;
+    if ((((uintptr_t)x & 15) == 0) && (K % 16 == 0)) {
+        const uint4* x4 = reinterpret_cast<const uint4*>(x);
+        for (uint64_t i = lane; i < K / 16; i += 32) {
+            uint4 v = __ldg(x4 + i);
+            acc = __dp4a((int)v.x, 0x01010101, acc);
+            acc = __dp4a((int)v.y, 0x01010101, acc);
+            acc = __dp4a((int)v.z, 0x01010101, acc);
+            acc = __dp4a((int)v.w, 0x01010101, acc);
+        }
+    } else {
+        for (uint64_t i = lane; i < K; i += 32) acc += (int32_t)x[i];
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) sums[row] = acc;
+}
+
+// scale = absmax / 127.0f (src/rpl_quantization.c:87-88) from the value the GEMM epilogue accumulated.
+__global__ void absmax_to_scale_kernel(const float* __restrict__ absmax, float* __restrict__ scale) {
+    *scale = __fdiv_rn(*absmax, 127.0f);
+}
+
+static int launch_row_sums(const int8_t* X, int32_t* sums, uint64_t rows, uint64_t K, cudaStream_t st) {
+    const unsigned int warps = 8;
+    row_sums_i8_kernel<<<(unsigned int)((rows + warps - 1) / warps), warps * 32, 0, st>>>(X, sums, rows, K);
+    return launched("row_sums_i8_kernel");
+}
+
 static int run_gemm(GemmProblem p, cudaStream_t st) {
     if (p.M == 0 || p.N == 0) return 0;
     if (!p.A || !p.B || !p.out) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null pointer");
@@ -39,17 +75,32 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
 
     GemmProblem q = p;
     const bool big = p.M * p.N * (p.K ? p.K : 1) >= kTcMinMacs;
-    if (p.b_is_kn && (backend >= 2 || big) && p.K % 16 == 0 && p.K && !(p.mode == EPI_REQUANT_I32 && (p.za || p.zb))) {
-        // Reorder B once into the K-contiguous layout the tensor-core kernel reads.
-        const uint64_t gy = (p.K + 31) / 32;
-        if (gy <= 65535) {
-            Scratch sc;
-            if (int rc = scratch_for(st, (size_t)(p.K * p.N), &sc)) return rc;
-            dim3 grid((unsigned int)((p.N + 31) / 32), (unsigned int)gy), block(32, 8);
-            transpose_i8_kernel<<<grid, block, 0, st>>>(p.B, static_cast<int8_t*>(sc.data), p.K, p.N);
+    const bool want_tc = (backend >= 2 || big) && p.K && p.K % 16 == 0;
+    const bool zero_points = p.mode == EPI_REQUANT_I32 && (p.za || p.zb);
+    if (want_tc && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535 &&
+        p.M <= 0x7fffffffull * 8 && p.N <= 0x7fffffffull * 8) {
+        // Library scratch: [ B as [N,K] | row sums of A | column sums of B ].
+        const size_t bt_bytes = p.b_is_kn ? (((size_t)(p.K * p.N) + 255) & ~(size_t)255) : 0;
+        const size_t rs_bytes = zero_points ? (((size_t)p.M * 4 + 255) & ~(size_t)255) : 0;
+        const size_t cs_bytes = zero_points ? (size_t)p.N * 4 : 0;
+        Scratch sc;
+        if (int rc = scratch_for(st, bt_bytes + rs_bytes + cs_bytes, &sc)) return rc;
+        char* base = static_cast<char*>(sc.data);
+        if (p.b_is_kn) {
+            // Reorder B once into the K-contiguous layout the tensor-core kernel reads.
+            dim3 grid((unsigned int)((p.N + 31) / 32), (unsigned int)((p.K + 31) / 32)), block(32, 8);
+            transpose_i8_kernel<<<grid, block, 0, st>>>(p.B, reinterpret_cast<int8_t*>(base), p.K, p.N);
             if (int rc = launched("transpose_i8_kernel")) return rc;
-            q.B = static_cast<const int8_t*>(sc.data);
+            q.B = reinterpret_cast<const int8_t*>(base);
             q.b_is_kn = 0;
+        }
+        if (zero_points && !q.b_is_kn) {
+            int32_t* rs = reinterpret_cast<int32_t*>(base + bt_bytes);
+            int32_t* cs = reinterpret_cast<int32_t*>(base + bt_bytes + rs_bytes);
+            if (int rc = launch_row_sums(q.A, rs, p.M, p.K, st)) return rc;
+            if (int rc = launch_row_sums(q.B, cs, p.N, p.K, st)) return rc;      // rows of [N,K] = columns of B
+            q.a_row_sums = rs;
+            q.b_col_sums = cs;
         }
     }
     if (backend >= 2) return gemm_tcgen05(q, st, backend - 2);
@@ -95,6 +146,36 @@ int rplb_linear_i8_dequant_f32(const int8_t* x, const int8_t* w, float* out, uin
     p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
     p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
     p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu;
+    return run_gemm(p, as_stream(stream));
+}
+
+int rplb_linear_i8_dequant_f32_absmax(const int8_t* x, const int8_t* w, float* out, uint64_t M, uint64_t K, uint64_t N,
+                                      uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
+                                      int relu, float* absmax, float* next_scale, void* stream) {
+    if (!a_scale || !w_scales || !absmax) return fail(RPLB_E_BAD_ARG, "rplb_linear_i8_dequant_f32_absmax: null pointer");
+    cudaStream_t st = as_stream(stream);
+    if (int rc = cuda_ok(cudaMemsetAsync(absmax, 0, sizeof(float), st), "cudaMemsetAsync(absmax)")) return rc;
+    GemmProblem p = {};
+    p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+    p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
+    p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu; p.absmax_out = absmax;
+    if (int rc = run_gemm(p, st)) return rc;
+    if (next_scale) {
+        absmax_to_scale_kernel<<<1, 1, 0, st>>>(absmax, next_scale);
+        return launched("absmax_to_scale_kernel");
+    }
+    return 0;
+}
+
+int rplb_linear_i8_requant_i8(const int8_t* x, const int8_t* w, int8_t* out, uint64_t M, uint64_t K, uint64_t N,
+                              uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
+                              int relu, const float* out_scale, int32_t out_zero_point, void* stream) {
+    if (!a_scale || !w_scales || !out_scale) return fail(RPLB_E_BAD_ARG, "rplb_linear_i8_requant_i8: null scale pointer");
+    GemmProblem p = {};
+    p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+    p.b_is_kn = 0; p.mode = EPI_DEQUANT_I8;
+    p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu;
+    p.out_scale = out_scale; p.out_zp = out_zero_point;
     return run_gemm(p, as_stream(stream));
 }
 

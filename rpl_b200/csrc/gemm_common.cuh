@@ -9,6 +9,7 @@ enum EpilogueMode : int {
     EPI_RAW_I32 = 0,      // linear_int8: raw accumulator (+ int8 bias)      src/rpl_quantization.c:346-350
     EPI_REQUANT_I32 = 1,  // gemm_int8: roundf(sum*sa*sb/sc) as int32        src/ops_extended.c:119-120
     EPI_DEQUANT_F32 = 2,  // fused fp32: ((float)acc*sA)*sW[n] + bias[n], optional ReLU
+    EPI_DEQUANT_I8 = 3,   // the same fp32 value quantized straight to int8 with a given output scale / zero point
 };
 
 struct GemmProblem {
@@ -23,11 +24,17 @@ struct GemmProblem {
     // EPI_REQUANT_I32
     float sa, sb, sc;
     int32_t za, zb;
+    const int32_t* a_row_sums;   // sum_k A[m,k], needed by kernels that cannot subtract zero points in the loop
+    const int32_t* b_col_sums;   // sum_k B[k,n]
     // EPI_DEQUANT_F32
     const float* a_scale;     // one float on the device
     const float* w_scales;    // N floats
     const float* bias_f32;    // N floats or null
     int relu;
+    float* absmax_out;        // optional: max |out| over the call is folded in here (bits of a non-negative float)
+    // EPI_DEQUANT_I8
+    const float* out_scale;   // one float on the device
+    int32_t out_zp;
 };
 
 #ifdef __CUDACC__
@@ -49,6 +56,28 @@ __device__ __forceinline__ float dequant_f32(int32_t acc, float a_scale, float w
     if (has_bias) v = __fadd_rn(v, bias);
     if (relu && v < 0.0f) v = 0.0f;
     return v;
+}
+#endif
+
+#ifdef __CUDACC__
+// sum_k (a-za)(b-zb) from the plain product and the row / column sums, mod 2^32.
+__device__ __forceinline__ int32_t apply_zero_points(int32_t sum, int32_t row_sum, int32_t col_sum, int32_t za, int32_t zb, uint32_t K) {
+    uint32_t s = (uint32_t)sum;
+    s -= (uint32_t)zb * (uint32_t)row_sum;
+    s -= (uint32_t)za * (uint32_t)col_sum;
+    s += K * (uint32_t)za * (uint32_t)zb;
+    return (int32_t)s;
+}
+
+// Folds |v| into a running maximum kept as the bit pattern of a non-negative
+// float (such patterns order like unsigned integers).  NaN is skipped, as the
+// reference's min/max compares skip it.
+__device__ __forceinline__ void absmax_fold(float& running, float v) {
+    running = fmaxf(running, fabsf(v));         // fmaxf returns the other operand for a NaN
+}
+__device__ __forceinline__ void absmax_publish(float* dst, float running) {
+    running = warp_max(running);
+    if ((threadIdx.x & 31) == 0 && running > 0.0f) atomicMax(reinterpret_cast<unsigned int*>(dst), __float_as_uint(running));
 }
 #endif
 

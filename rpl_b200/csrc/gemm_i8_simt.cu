@@ -96,7 +96,10 @@ gemm_i8_simt_kernel(GemmProblem p) {
         __syncthreads();
     }
 
-    const float a_scale = (p.mode == EPI_DEQUANT_F32) ? __ldg(p.a_scale) : 0.0f;
+    const bool fp_mode = p.mode == EPI_DEQUANT_F32 || p.mode == EPI_DEQUANT_I8;
+    const float a_scale = fp_mode ? __ldg(p.a_scale) : 0.0f;
+    const QuantConsts oq = make_quant_consts(p.mode == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
+    float absmax = 0.0f;
     #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint64_t m = m0 + ty * 4 + i;
@@ -106,14 +109,7 @@ gemm_i8_simt_kernel(GemmProblem p) {
             const uint64_t n = n0 + tx + 16 * j;
             if (n >= p.N) continue;
             int32_t sum = acc[i][j];
-            if (ZERO_POINTS) {
-                // sum_k (a-za)(b-zb) = sum ab - zb*sum a - za*sum b + K*za*zb   (mod 2^32)
-                uint32_t s = (uint32_t)sum;
-                s -= (uint32_t)p.zb * (uint32_t)rowsum[i];
-                s -= (uint32_t)p.za * (uint32_t)colsum[j];
-                s += (uint32_t)p.K * (uint32_t)p.za * (uint32_t)p.zb;
-                sum = (int32_t)s;
-            }
+            if (ZERO_POINTS) sum = apply_zero_points(sum, rowsum[i], colsum[j], p.za, p.zb, (uint32_t)p.K);
             const uint64_t o = m * p.ldo + n;
             if (p.mode == EPI_RAW_I32) {
                 if (p.bias_i8) sum = (int32_t)((uint32_t)sum + (uint32_t)(int32_t)__ldg(p.bias_i8 + n));
@@ -121,11 +117,15 @@ gemm_i8_simt_kernel(GemmProblem p) {
             } else if (p.mode == EPI_REQUANT_I32) {
                 static_cast<int32_t*>(p.out)[o] = requant_i32(sum, p.sa, p.sb, p.sc);
             } else {
-                static_cast<float*>(p.out)[o] = dequant_f32(sum, a_scale, __ldg(p.w_scales + n), p.bias_f32 != nullptr,
-                                                            p.bias_f32 ? __ldg(p.bias_f32 + n) : 0.0f, p.relu != 0);
+                const float v = dequant_f32(sum, a_scale, __ldg(p.w_scales + n), p.bias_f32 != nullptr,
+                                            p.bias_f32 ? __ldg(p.bias_f32 + n) : 0.0f, p.relu != 0);
+                if (p.absmax_out) absmax_fold(absmax, v);
+                if (p.mode == EPI_DEQUANT_F32) static_cast<float*>(p.out)[o] = v;
+                else static_cast<int8_t*>(p.out)[o] = (int8_t)quantize_one(v, oq.scale, oq.zp);
             }
         }
     }
+    if (fp_mode && p.absmax_out) absmax_publish(p.absmax_out, absmax);
 }
 
 int gemm_simt(const GemmProblem& p, cudaStream_t st) {

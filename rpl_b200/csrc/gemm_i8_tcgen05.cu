@@ -167,30 +167,50 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
 
 // --------------------------------------------------------------------------- epilogue of one 32-column chunk
 // Thread = one output row m; r[0..31] = accumulators of columns n_first..n_first+31.
+// s_scales / s_aux: this warp's shared-memory copies of the per-column values of
+// the chunk (weight scales and bias for the fp32 modes; s_aux holds the column
+// sums, as int32 bit patterns, when gemm_int8 runs with zero points).
 template <int MODE>
 __device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t (&r)[32], uint64_t m, uint64_t n_first,
-                                            float a_scale, const float* s_scales, const float* s_bias) {
+                                            float a_scale, const float* s_scales, const float* s_aux,
+                                            const QuantConsts& oq, int32_t row_sum, float& absmax) {
     if (m >= p.M) return;
     const uint64_t n_left = p.N - n_first;          // caller guarantees n_first < N
-    if (MODE == EPI_DEQUANT_F32) {
-        float* row = static_cast<float*>(p.out) + m * p.ldo + n_first;
+    const bool full = n_left >= 32;
+    if (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) {
         const bool has_bias = p.bias_f32 != nullptr;
         const bool relu = p.relu != 0;
-        if (n_left >= 32 && (((uintptr_t)row & 15) == 0)) {
-            #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-                float4 v;
-                v.x = dequant_f32((int32_t)r[c + 0], a_scale, s_scales[c + 0], has_bias, s_bias[c + 0], relu);
-                v.y = dequant_f32((int32_t)r[c + 1], a_scale, s_scales[c + 1], has_bias, s_bias[c + 1], relu);
-                v.z = dequant_f32((int32_t)r[c + 2], a_scale, s_scales[c + 2], has_bias, s_bias[c + 2], relu);
-                v.w = dequant_f32((int32_t)r[c + 3], a_scale, s_scales[c + 3], has_bias, s_bias[c + 3], relu);
-                __stcs(reinterpret_cast<float4*>(row + c), v);
-            }
-        } else {
+        float v[32];
+        #pragma unroll
+        for (int c = 0; c < 32; c++) v[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[c], has_bias, s_aux[c], relu);
+        if (p.absmax_out) {
             #pragma unroll
             for (int c = 0; c < 32; c++)
-                if ((uint64_t)c < n_left)
-                    row[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[c], has_bias, s_bias[c], relu);
+                if (full || (uint64_t)c < n_left) absmax_fold(absmax, v[c]);
+        }
+        if (MODE == EPI_DEQUANT_F32) {
+            float* row = static_cast<float*>(p.out) + m * p.ldo + n_first;
+            if (full && (((uintptr_t)row & 15) == 0)) {
+                #pragma unroll
+                for (int c = 0; c < 32; c += 4) __stcs(reinterpret_cast<float4*>(row + c), make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]));
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 32; c++)
+                    if ((uint64_t)c < n_left) row[c] = v[c];
+            }
+        } else {
+            int8_t* row = static_cast<int8_t*>(p.out) + m * p.ldo + n_first;
+            uint32_t w[8];
+            #pragma unroll
+            for (int c = 0; c < 8; c++) w[c] = quantize_quad_packed(make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]), oq);
+            if (full && (((uintptr_t)row & 15) == 0)) {
+                __stcs(reinterpret_cast<uint4*>(row), make_uint4(w[0], w[1], w[2], w[3]));
+                __stcs(reinterpret_cast<uint4*>(row + 16), make_uint4(w[4], w[5], w[6], w[7]));
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 32; c++)
+                    if ((uint64_t)c < n_left) row[c] = (int8_t)((w[c >> 2] >> (8 * (c & 3))) & 0xff);
+            }
         }
     } else {
         int32_t* row = static_cast<int32_t*>(p.out) + m * p.ldo + n_first;
@@ -201,11 +221,12 @@ __device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t
             if (MODE == EPI_RAW_I32) {
                 if (p.bias_i8 && (uint64_t)c < n_left) s = (int32_t)((uint32_t)s + (uint32_t)(int32_t)__ldg(p.bias_i8 + n_first + c));
             } else {
+                if (p.a_row_sums) s = apply_zero_points(s, row_sum, __float_as_int(s_aux[c]), p.za, p.zb, (uint32_t)p.K);
                 s = requant_i32(s, p.sa, p.sb, p.sc);
             }
             v[c] = s;
         }
-        if (n_left >= 32 && (((uintptr_t)row & 15) == 0)) {
+        if (full && (((uintptr_t)row & 15) == 0)) {
             #pragma unroll
             for (int c = 0; c < 32; c += 4)
                 __stcs(reinterpret_cast<int4*>(row + c), make_int4(v[c], v[c + 1], v[c + 2], v[c + 3]));
@@ -213,6 +234,29 @@ __device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t
             #pragma unroll
             for (int c = 0; c < 32; c++)
                 if ((uint64_t)c < n_left) row[c] = v[c];
+        }
+    }
+}
+
+// Per-tile staging of the per-column epilogue inputs into this warp's shared-memory slots.
+template <int MODE>
+__device__ __forceinline__ void stage_columns(const GemmProblem& p, uint64_t n0, int lane, float* s_scales, float* s_aux) {
+    if (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) {
+        __syncwarp();
+        for (int c = lane; c < TILE_N; c += 32) {
+            const uint64_t n = n0 + c;
+            s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
+            s_aux[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
+        }
+        __syncwarp();
+    } else if (MODE == EPI_REQUANT_I32) {
+        if (p.b_col_sums) {
+            __syncwarp();
+            for (int c = lane; c < TILE_N; c += 32) {
+                const uint64_t n = n0 + c;
+                s_aux[c] = __int_as_float(n < p.N ? __ldg(p.b_col_sums + n) : 0);
+            }
+            __syncwarp();
         }
     }
 }
@@ -299,22 +343,17 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int ew = warp - kEpilogueWarp0;
         float* s_scales = sh->w_scales + ew * TILE_N;
         float* s_bias = sh->bias + ew * TILE_N;
-        const float a_scale = (MODE == EPI_DEQUANT_F32) ? __ldg(p.a_scale) : 0.0f;
+        const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
+        const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
+        float absmax = 0.0f;
         uint32_t acc = 0, acc_phase = 0;
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
             const uint64_t m = (uint64_t)tm * TILE_M + quarter * 32 + lane;
-            if (MODE == EPI_DEQUANT_F32) {
-                __syncwarp();
-                for (int c = lane; c < TILE_N; c += 32) {
-                    const uint64_t n = n0 + c;
-                    s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
-                    s_bias[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
-                }
-                __syncwarp();
-            }
+            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -326,13 +365,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
                 tc_wait_ld();
-                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32);
+                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
             if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
         }
+        if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
     }
 
     // ----------------------------------------------------------------- teardown
@@ -506,22 +546,17 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int ew = warp - kEpilogueWarp0;
         float* s_scales = sh->w_scales + ew * TILE_N;
         float* s_bias = sh->bias + ew * TILE_N;
-        const float a_scale = (MODE == EPI_DEQUANT_F32) ? __ldg(p.a_scale) : 0.0f;
+        const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
+        const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
+        float absmax = 0.0f;
         uint32_t acc = 0, acc_phase = 0;
         for (uint32_t tile = pair; tile < total_tiles; tile += num_pairs) {
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
             const uint64_t m = (uint64_t)tm * PAIR_TILE_M + cta * 128 + quarter * 32 + lane;
-            if (MODE == EPI_DEQUANT_F32) {
-                __syncwarp();
-                for (int c = lane; c < TILE_N; c += 32) {
-                    const uint64_t n = n0 + c;
-                    s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
-                    s_bias[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
-                }
-                __syncwarp();
-            }
+            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -533,13 +568,14 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
                 tc_wait_ld();
-                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32);
+                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->acc_empty[acc]), 0));
             if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
         }
+        if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
     }
 
     // ----------------------------------------------------------------- teardown
@@ -597,7 +633,8 @@ bool gemm_tcgen05_supports(const GemmProblem& p) {
     if (p.M == 0 || p.N == 0 || p.K == 0) return false;
     if (p.K % 16 != 0) return false;                              // TMA: row stride in multiples of 16 bytes
     if (((uintptr_t)p.A & 15) || ((uintptr_t)p.B & 15)) return false;
-    if (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0)) return false;
+    // zero points need the row sums of A and the column sums of B for the epilogue correction
+    if (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0) && !(p.a_row_sums && p.b_col_sums)) return false;
     if (p.M > 0x7fffffffull || p.N > 0x7fffffffull || p.K > 0x7fffffffull) return false;
     const uint64_t tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
     return tiles < 0x7fffffffull;
@@ -693,7 +730,7 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const Ge
 // variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = CTA pair per 256 x 256 tile.
 int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     if (!gemm_tcgen05_supports(p))
-        return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W, zero points 0");
+        return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W");
     if (int prev = gemm_tcgen05_status(true))
         return fail(RPLB_E_KERNEL, "an earlier tcgen05 GEMM gave up waiting (code %d)", prev);
     int* status_host = kernel_status_word();
@@ -723,6 +760,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
             case EPI_RAW_I32:     return launch_tc_pair<EPI_RAW_I32>(ma, mw, p, num_kb, status_dev, st);
             case EPI_REQUANT_I32: return launch_tc_pair<EPI_REQUANT_I32>(ma, mw, p, num_kb, status_dev, st);
             case EPI_DEQUANT_F32: return launch_tc_pair<EPI_DEQUANT_F32>(ma, mw, p, num_kb, status_dev, st);
+            case EPI_DEQUANT_I8:  return launch_tc_pair<EPI_DEQUANT_I8>(ma, mw, p, num_kb, status_dev, st);
         }
         return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
     }
@@ -736,6 +774,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
         case EPI_REQUANT_I32: return launch_tc<EPI_REQUANT_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
         case EPI_DEQUANT_F32: return launch_tc<EPI_DEQUANT_F32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+        case EPI_DEQUANT_I8:  return launch_tc<EPI_DEQUANT_I8>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
     }
     return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
 }

@@ -184,3 +184,42 @@ def linear_i8_dequant(x, w, a_scale, w_scales, bias=None, relu=False, out=None):
     capi.call("rplb_linear_i8_dequant_f32", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
               _p(bias), 1 if relu else 0, _stream())
     return out
+
+
+def linear_i8_dequant_absmax(x, w, a_scale, w_scales, bias=None, relu=False, out=None):
+    """``linear_i8_dequant`` that also returns ``(absmax, next_scale)``: max |out| and
+    absmax / 127, the per-tensor symmetric scale of ``out``, both one-element device
+    tensors, so the next layer can quantize ``out`` without a min/max pass."""
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    M, K = x.shape
+    N = w.shape[0]
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    stats = torch.empty(2, dtype=torch.float32, device=x.device)
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    capi.call("rplb_linear_i8_dequant_f32_absmax", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
+              _p(bias), 1 if relu else 0, _p(stats[0:1]), _p(stats[1:2]), _stream())
+    return out, stats[0:1], stats[1:2]
+
+
+def linear_i8_requant_i8(x, w, a_scale, w_scales, out_scale, out_zero_point=0, bias=None, relu=False, out=None):
+    """Fused layer with int8 output: the fp32 epilogue value quantized with a given
+    (calibrated) scale, as tensor_quantize_int8 would; ``out_scale`` is a one-element
+    device tensor."""
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    M, K = x.shape
+    N = w.shape[0]
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=x.device)
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    capi.call("rplb_linear_i8_requant_i8", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
+              _p(bias), 1 if relu else 0, _p(out_scale), int(out_zero_point), _stream())
+    return out

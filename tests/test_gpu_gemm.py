@@ -197,3 +197,60 @@ def test_sampled_tiles_vs_checker_at_projection_size(cuda, lib, port, backend):
         m0, n0 = int(rng.integers(0, M - 128)), int(rng.integers(0, N - 128))
         want = port.linear(host(A[m0:m0 + 128]), host(W[n0:n0 + 128]))
         assert same(host(Cd[m0:m0 + 128, n0:n0 + 128]), want)
+
+
+@pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (64, 40, 16)])
+@pytest.mark.parametrize("which", [TC_SINGLE, TC_PAIR])
+def test_zero_points_on_the_tensor_core_path(cuda, lib, port, backend, mnk, which):
+    """gemm_int8 with za, zb != 0: the tensor-core kernels correct the plain product
+    with row sums of A and column sums of B in the epilogue."""
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M + 2 * N + 3 * K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    D.gemm_backend(which)
+    for args in ((0.013, 0.021, 0.37, 3, -7), (1, 1, 1, -128, 127), (0.3, 0.3, 1e-4, 5, 0), (1, 1, 1, 0, 9)):
+        got = host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda), *args))
+        assert same(got, port.gemm_requant(A, B, *args)), args
+
+
+@pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (65, 10, 128)])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+def test_epilogue_reports_absmax_for_the_next_layer(cuda, lib, port, backend, mnk, which):
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 11 + N)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 2e-4).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    a_dev = dev(np.array([0.0231], np.float32), cuda)
+    D.gemm_backend(which)
+    for relu in (False, True):
+        out, absmax, scale = D.linear_i8_dequant_absmax(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda), dev(bias, cuda), relu)
+        want = port.linear_dequant(A, W, np.float32(0.0231), ws, bias, relu)
+        assert same(host(out), want)
+        wq, wscale = port.quantize_symmetric(want)
+        assert same(host(scale)[0], wscale) and float(absmax.item()) == float(np.abs(want).max())
+        # the next layer's quantizer, fed the reported scale, reproduces the two-pass result
+        assert same(host(D.quantize_dev(out, scale)), wq)
+
+
+@pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (65, 10, 128), (256, 256, 256)])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+def test_int8_output_with_a_static_scale(cuda, lib, port, backend, mnk, which):
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 13 + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 2e-4).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    a_dev = dev(np.array([0.0231], np.float32), cuda)
+    D.gemm_backend(which)
+    for out_scale, zp, relu in ((0.05, 0, True), (0.031, -9, False), (1e-3, 4, False)):
+        want = port.quantize(port.linear_dequant(A, W, np.float32(0.0231), ws, bias, relu), np.float32(out_scale), zp)
+        got = D.linear_i8_requant_i8(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda),
+                                     dev(np.array([out_scale], np.float32), cuda), zp, dev(bias, cuda), relu)
+        assert same(host(got), want), (out_scale, zp, relu)
