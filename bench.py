@@ -486,14 +486,23 @@ def run_secondary(a):
         h, hq, ph = torch.empty((Bn, 128), device=dev), torch.empty((Bn, 128), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
         logits = torch.empty((Bn, 10), device=dev)
         ops = 2.0 * Bn * (784 * 128 + 128 * 10)
-        # X read twice (min/max, quantize) + int8 X written and read + hidden fp32/int8 + logits
-        hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4 + 4 + 1 + 1) + 10 * 4)
+        # X read twice (min/max, quantize) + int8 X written and read + hidden fp32 written and read once,
+        # int8 hidden written and read + logits
+        hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4 + 1 + 1) + 10 * 4)
+
+        stats = torch.empty(2, device=dev)
+        import ctypes as C
+        from rpl_b200 import capi
 
         def step():
             D.quantize_symmetric(X, out=xq, params=px)
-            D.linear_i8_dequant(xq, w1q, one(px), w1s, b1, relu=True, out=h)
-            D.quantize_symmetric(h, out=hq, params=ph)
-            D.linear_i8_dequant(hq, w2q, one(ph), w2s, b2, relu=False, out=logits)
+            # layer 1: fused dequant + bias + ReLU; the epilogue also reports max|h| and the scale of h
+            capi.call("rplb_linear_i8_dequant_f32_absmax", C.c_void_p(xq.data_ptr()), C.c_void_p(w1q.data_ptr()),
+                      C.c_void_p(h.data_ptr()), Bn, 784, 128, 128, C.c_void_p(one(px).data_ptr()),
+                      C.c_void_p(w1s.data_ptr()), C.c_void_p(b1.data_ptr()), 1, C.c_void_p(stats[0:1].data_ptr()),
+                      C.c_void_p(stats[1:2].data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            D.quantize_dev(h, stats[1:2], out=hq)
+            D.linear_i8_dequant(hq, w2q, stats[1:2], w2s, b2, relu=False, out=logits)
         note = "HBM-bound: 13.3 GOP over ~0.7 GB of traffic"
     else:
         name = "transformer projections: tokens 32768 x d_model 4096, Q/K/V/O weights 4096x4096 per channel, bias, fp32 out"
@@ -510,14 +519,27 @@ def run_secondary(a):
             for (wq, wsc, _), b, o in zip(ws_, bs, outs):
                 D.linear_i8_dequant(xq, wq, one(px), wsc, b, out=o)
         note = "X quantized once per step, four GEMMs with fused per-channel dequant + bias"
-    for _ in range(max(a.warmup, 3)):
+    # These steps are a handful of short kernels: replay them from a CUDA graph so
+    # that the host's launch cost does not show up as GPU idle time.  The library
+    # allocates its per-stream scratch on first use, so warm up on the capture stream.
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(a.warmup, 3)):
+            step()
+    side.synchronize()
+    l0 = D.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
         step()
+    per_step = D.launch_count() - l0
+    for _ in range(3):
+        graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    l0 = D.launch_count()
     e0.record()
     for _ in range(a.steps):
-        step()
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
     if D.kernel_status(True) != 0:
@@ -525,8 +547,8 @@ def run_secondary(a):
     ms = e0.elapsed_time(e1) / a.steps
     line = {"metric": METRIC, "value": ops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1, "steps": a.steps,
             "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": {"workload": name, "note": note},
-            "gpu_launches": int(D.launch_count() - l0)}
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": {"workload": name, "note": note, "replay": "CUDA graph of one step"},
+            "gpu_launches": int(per_step * a.steps)}
     if hbm_bytes:
         gbs = hbm_bytes / (ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
