@@ -350,6 +350,16 @@ void    linear_int8_dequant(const QuantizedTensor* x, const PerChannelQuantizedT
                             float* out, uint32_t batch_size, uint32_t in_features, uint32_t out_features,
                             bool relu);
 
+/* Quantized weights on disk, in the framing of the reference's fp32 checkpoint
+ * writer (checkpoint_save_model, src/rpl_training.c:915-944; the reference has
+ * no loader and no int8 format): header {count, tag "INT8", 0.0f}, then per
+ * tensor dims, shape[dims], size, int8 data[size], num_channels, fp32
+ * scales[num_channels].  save returns 0 on success; load returns a malloc'ed
+ * array of *num_tensors tensors in host memory, or in device memory when
+ * to_device is true (NULL on error). */
+int     quantized_weights_save(const char* path, PerChannelQuantizedTensor* const* tensors, uint32_t num_tensors);
+PerChannelQuantizedTensor** quantized_weights_load(const char* path, uint32_t* num_tensors, bool to_device);
+
 /* out = (float)q * scales[channel], a new fp32 Tensor shaped like the input. */
 Tensor* tensor_dequantize_per_channel(const PerChannelQuantizedTensor* input);
 

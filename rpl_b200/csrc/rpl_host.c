@@ -533,3 +533,105 @@ void quantized_model_free(QuantizedModel* qm) {
     free(qm->int8_params);
     free(qm);
 }
+
+/* ------------------------------------------------------------------------
+ * Quantized weights on disk.
+ *
+ * The reference only writes fp32 checkpoints (checkpoint_save_model,
+ * src/rpl_training.c:915-944) and has no loader.  The file written here keeps
+ * that framing -- a three-word header, then per tensor `dims, shape[dims],
+ * size, data[size]` -- with two changes that make it self-describing: the
+ * header's second word (the reference's epoch) holds the tag 0x38544E49
+ * ("INT8"), and each tensor's data is `size` int8 values followed by
+ * `num_channels` and that many fp32 scales.  Zero points are not stored: the
+ * per-channel quantizer only produces zero (src/rpl_quantization.c:148).
+ * ---------------------------------------------------------------------- */
+#define RPL_INT8_FILE_TAG 0x38544E49u
+
+int quantized_weights_save(const char* path, PerChannelQuantizedTensor* const* tensors, uint32_t num_tensors) {
+    if (!path || (!tensors && num_tensors)) return -1;
+    FILE* f = fopen(path, "wb");
+    if (!f) return -1;
+    uint32_t tag = RPL_INT8_FILE_TAG;
+    float zero = 0.0f;
+    int ok = fwrite(&num_tensors, 4, 1, f) == 1 && fwrite(&tag, 4, 1, f) == 1 && fwrite(&zero, 4, 1, f) == 1;
+    for (uint32_t i = 0; ok && i < num_tensors; i++) {
+        const PerChannelQuantizedTensor* t = tensors[i];
+        const size_t n = (size_t)t->num_channels * t->channel_size;
+        uint32_t size = (uint32_t)n;
+        int8_t* data = t->data;
+        float* scales = t->scales;
+        void *tmp_d = NULL, *tmp_s = NULL;
+        if (on_device(t->data)) {           /* device-resident weights are fetched first */
+            tmp_d = malloc(n ? n : 1);
+            tmp_s = malloc(t->num_channels ? (size_t)t->num_channels * 4 : 4);
+            ok = tmp_d && tmp_s && report(rplb_copy(tmp_d, t->data, n, NULL), "quantized_weights_save") == 0 &&
+                 report(rplb_copy(tmp_s, t->scales, (size_t)t->num_channels * 4, NULL), "quantized_weights_save") == 0 &&
+                 finish("quantized_weights_save") == 0;
+            data = (int8_t*)tmp_d;
+            scales = (float*)tmp_s;
+        }
+        ok = ok && fwrite(&t->dims, 4, 1, f) == 1 && fwrite(t->shape, 4, t->dims, f) == t->dims &&
+             fwrite(&size, 4, 1, f) == 1 && fwrite(data, 1, n, f) == n &&
+             fwrite(&t->num_channels, 4, 1, f) == 1 && fwrite(scales, 4, t->num_channels, f) == t->num_channels;
+        free(tmp_d);
+        free(tmp_s);
+    }
+    ok = (fclose(f) == 0) && ok;
+    return ok ? 0 : -1;
+}
+
+/* Reads a file written by quantized_weights_save.  Returns a malloc'ed array of
+ * *num_tensors tensors (each released with per_channel_quantized_tensor_free,
+ * the array with free), in host memory, or in device memory when to_device is
+ * true.  NULL on any error (bad tag, short file, allocation or copy failure). */
+PerChannelQuantizedTensor** quantized_weights_load(const char* path, uint32_t* num_tensors, bool to_device) {
+    if (!path || !num_tensors) return NULL;
+    FILE* f = fopen(path, "rb");
+    if (!f) return NULL;
+    uint32_t n_t = 0, tag = 0;
+    float metric;
+    if (fread(&n_t, 4, 1, f) != 1 || fread(&tag, 4, 1, f) != 1 || fread(&metric, 4, 1, f) != 1 ||
+        tag != RPL_INT8_FILE_TAG || n_t > (1u << 20)) { fclose(f); return NULL; }
+    PerChannelQuantizedTensor** out = (PerChannelQuantizedTensor**)calloc(n_t ? n_t : 1, sizeof(*out));
+    int ok = out != NULL;
+    for (uint32_t i = 0; ok && i < n_t; i++) {
+        PerChannelQuantizedTensor* t = (PerChannelQuantizedTensor*)calloc(1, sizeof(*t));
+        out[i] = t;
+        uint32_t size = 0;
+        ok = t && fread(&t->dims, 4, 1, f) == 1 && t->dims <= MAX_DIMS &&
+             fread(t->shape, 4, t->dims, f) == t->dims && fread(&size, 4, 1, f) == 1;
+        if (!ok) break;
+        /* The tensor owns its blocks from the moment they exist, so the error path below frees them. */
+        t->data = (int8_t*)rpitorch_aligned_alloc(64, size ? size : 1);
+        ok = t->data && fread(t->data, 1, size, f) == size && fread(&t->num_channels, 4, 1, f) == 1 &&
+             t->num_channels <= size + 1u;
+        if (!ok) break;
+        const size_t cb = t->num_channels ? (size_t)t->num_channels * 4 : 4;
+        t->scales = (float*)malloc(cb);
+        t->zero_points = (int32_t*)calloc(1, cb);
+        ok = t->scales && t->zero_points && fread(t->scales, 4, t->num_channels, f) == t->num_channels;
+        if (!ok) break;
+        t->channel_size = t->num_channels ? size / t->num_channels : 0;
+        if (to_device) {
+            void *dd = NULL, *ds = NULL, *dz = NULL;
+            ok = report(rplb_malloc(&dd, size), "quantized_weights_load") == 0 &&
+                 report(rplb_malloc(&ds, cb), "quantized_weights_load") == 0 &&
+                 report(rplb_malloc(&dz, cb), "quantized_weights_load") == 0 &&
+                 report(rplb_copy(dd, t->data, size, NULL), "quantized_weights_load") == 0 &&
+                 report(rplb_copy(ds, t->scales, (size_t)t->num_channels * 4, NULL), "quantized_weights_load") == 0 &&
+                 report(rplb_copy(dz, t->zero_points, (size_t)t->num_channels * 4, NULL), "quantized_weights_load") == 0 &&
+                 finish("quantized_weights_load") == 0;
+            if (!ok) { rplb_free(dd); rplb_free(ds); rplb_free(dz); break; }
+            free(t->data); free(t->scales); free(t->zero_points);
+            t->data = (int8_t*)dd; t->scales = (float*)ds; t->zero_points = (int32_t*)dz;
+        }
+    }
+    fclose(f);
+    if (!ok) {
+        if (out) { for (uint32_t i = 0; i < n_t; i++) per_channel_quantized_tensor_free(out[i]); free(out); }
+        return NULL;
+    }
+    *num_tensors = n_t;
+    return out;
+}
