@@ -44,10 +44,11 @@ def kernel_status(clear=True):
 
 
 # --------------------------------------------------------------------------- quantize / dequantize
-def minmax(x):
+def minmax(x, params=None):
     """Device ``rplb_qparams`` (8 words) of ``x``: see ``QPARAM_*`` indices."""
     _need(x, torch.float32, "x")
-    params = torch.empty(8, dtype=torch.float32, device=x.device)
+    if params is None:
+        params = torch.empty(8, dtype=torch.float32, device=x.device)
     capi.call("rplb_minmax_f32", _p(x), x.numel(), _p(params), _stream())
     return params
 

@@ -86,6 +86,7 @@ class ShardedQuantizedLinear:
         self._dev_in = None
         self._dev_out = None
         self._copy_stream = None
+        self._side = None
 
     @classmethod
     def from_fp32(cls, w_shard, bias=None, **kw):
@@ -148,6 +149,69 @@ class ShardedQuantizedLinear:
         """x: fp32 CUDA [M,K] -> fp32 column block [M, count] (quantize, then GEMM)."""
         xq, a_scale = self.quantize_activation(x)
         return self.gemm(xq, a_scale, out=out, row_chunks=row_chunks, after_chunk=after_chunk)
+
+    def activation_scale(self, x):
+        """The per-tensor symmetric scale of ``x`` (one-element device tensor) without
+        quantizing: the min/max pass only, row-sharded with one scalar all-reduce when
+        there is more than one rank."""
+        from . import device as D
+        M, K = x.shape
+        if self._xq is None or self._xq.shape != x.shape or self._xq.device != x.device:
+            self._xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+            self._params = torch.empty(8, dtype=torch.float32, device=x.device)
+        a_scale = self._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+        if self.world > 1 and self.shard_reduction and dist.is_initialized():
+            r0, rc = shard_range(M, self.world, self.rank, 1)
+            local = D.minmax(x[r0:r0 + rc])
+            pair = torch.stack((-local[D.QPARAM_MIN], local[D.QPARAM_MAX]))
+            dist.all_reduce(pair, op=dist.ReduceOp.MAX, group=self.group)
+            a_scale.copy_((torch.maximum(pair[0].abs(), pair[1].abs()) / 127.0).reshape(1))
+        else:
+            D.minmax(x, params=self._params)
+        return a_scale
+
+    def forward_overlapped(self, x, out=None, row_chunks=4, gemm_events=None):
+        """Same result as ``forward``; the quantize pass is pipelined under the GEMM.
+
+        The scale needs every element, so the min/max pass runs first.  After that
+        the quantize kernel (HBM-bound) and the GEMM (tensor-bound) want different
+        resources: the activation is quantized in ``row_chunks`` row blocks on a
+        second stream and the GEMM of a block starts as soon as that block is ready.
+        ``gemm_events``, if given, receives a (start, end) CUDA event pair per GEMM launch.
+        """
+        from . import device as D
+        M, K = x.shape
+        count = self.wq.shape[0]
+        if out is None:
+            out = torch.empty((M, count), dtype=torch.float32, device=x.device)
+        main = torch.cuda.current_stream(x.device)
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        a_scale = self.activation_scale(x)
+        ready = torch.cuda.Event()
+        ready.record(main)                      # scale known; every earlier reader of _xq is done
+        self._side.wait_event(ready)
+        step = (M + row_chunks - 1) // row_chunks
+        step = (step + 127) // 128 * 128
+        blocks = [(r0, min(M, r0 + step)) for r0 in range(0, M, step)]
+        blocks.reverse()                        # the end of x is what the min/max pass left in L2
+        done = []
+        with torch.cuda.stream(self._side):
+            for r0, r1 in blocks:
+                D.quantize_dev(x[r0:r1], a_scale, out=self._xq[r0:r1])
+                ev = torch.cuda.Event()
+                ev.record(self._side)
+                done.append(ev)
+        for (r0, r1), ev in zip(blocks, done):
+            main.wait_event(ev)
+            if gemm_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(main)
+            D.linear_i8_dequant(self._xq[r0:r1], self.wq, a_scale, self.w_scales, self.bias, self.relu, out=out[r0:r1])
+            if gemm_events is not None:
+                e1.record(main)
+                gemm_events.append((e0, e1))
+        return out
 
     def forward_host(self, x_host, out_host, row_chunks=8):
         """Host buffers in, host buffers out (page-locked for full PCIe speed).
