@@ -8,7 +8,7 @@ import pytest
 
 from conftest import ROOT
 
-REF_INCLUDE = "/root/reference/include"
+REF_INCLUDE = os.path.join(os.environ.get("RPL_REFERENCE", "/root/reference"), "include")
 SRC = os.path.join(ROOT, "tests", "c", "drop_in_check.c")
 
 
