@@ -34,7 +34,7 @@ gemm_i8_simt_kernel(GemmProblem p) {
     __shared__ uint32_t Bs[BN * LDW];
     const int t = threadIdx.x;
     const int tx = t & 15, ty = t >> 4;
-    const uint64_t m0 = (uint64_t)blockIdx.y * BM, n0 = (uint64_t)blockIdx.x * BN;
+    const uint64_t m0 = (uint64_t)blockIdx.x * BM, n0 = (uint64_t)blockIdx.y * BN;      // x spans M: it may be large
     const bool a_aligned = (((uintptr_t)p.A & 3) == 0) && (p.K % 4 == 0);
     const bool b_aligned = (((uintptr_t)p.B & 3) == 0) && (p.K % 4 == 0);
 
@@ -130,8 +130,9 @@ gemm_i8_simt_kernel(GemmProblem p) {
 
 int gemm_simt(const GemmProblem& p, cudaStream_t st) {
     if (p.M == 0 || p.N == 0) return 0;
-    uint64_t gx = (p.N + BN - 1) / BN, gy = (p.M + BM - 1) / BM;
-    if (gy > 65535) return fail(RPLB_E_TOO_LARGE, "dp4a GEMM: M = %llu exceeds 65535*64 rows", (unsigned long long)p.M);
+    uint64_t gx = (p.M + BM - 1) / BM, gy = (p.N + BN - 1) / BN;
+    if (gy > 65535 || gx > 0x7fffffffull)
+        return fail(RPLB_E_TOO_LARGE, "dp4a GEMM: N = %llu exceeds 65535*64 columns (or M beyond 2^37 rows)", (unsigned long long)p.N);
     dim3 grid((unsigned int)gx, (unsigned int)gy);
     if (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0))
         gemm_i8_simt_kernel<true><<<grid, SIMT_THREADS, 0, st>>>(p);

@@ -254,3 +254,22 @@ def test_int8_output_with_a_static_scale(cuda, lib, port, backend, mnk, which):
         got = D.linear_i8_requant_i8(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda),
                                      dev(np.array([out_scale], np.float32), cuda), zp, dev(bias, cuda), relu)
         assert same(host(got), want), (out_scale, zp, relu)
+
+
+def test_empty_and_degenerate_shapes(cuda, lib, port, backend):
+    D = backend
+    z = lambda *s: torch.zeros(s, dtype=torch.int8, device=cuda)
+    # K = 0: every sum is empty, the int8 bias still applies
+    b = dev(np.array([5, -7, 9], np.int8), cuda)
+    out = D.linear_i8(z(4, 0), z(3, 0), b)
+    assert host(out).tolist() == [[5, -7, 9]] * 4
+    # M = 0 and N = 0: nothing is written, nothing fails
+    assert D.linear_i8(z(0, 16), z(3, 16)).shape == (0, 3)
+    assert D.linear_i8(z(4, 16), z(0, 16)).shape == (4, 0)
+    assert D.gemm_i8_requant(z(0, 16), z(16, 5)).shape == (0, 5)
+    # a tall problem on the dp4a kernel (more than 65535 row tiles' worth would overflow a y grid)
+    rng = np.random.default_rng(0)
+    A = rng.integers(-128, 128, (70000 * 2, 20), dtype=np.int8)
+    W = rng.integers(-128, 128, (3, 20), dtype=np.int8)
+    D.gemm_backend(SIMT)
+    assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W))
