@@ -267,9 +267,9 @@ def test_empty_and_degenerate_shapes(cuda, lib, port, backend):
     assert D.linear_i8(z(0, 16), z(3, 16)).shape == (0, 3)
     assert D.linear_i8(z(4, 16), z(0, 16)).shape == (4, 0)
     assert D.gemm_i8_requant(z(0, 16), z(16, 5)).shape == (0, 5)
-    # a tall problem on the dp4a kernel (more than 65535 row tiles' worth would overflow a y grid)
+    # a tall problem on the dp4a kernel: more than 65535 row tiles
     rng = np.random.default_rng(0)
-    A = rng.integers(-128, 128, (70000 * 2, 20), dtype=np.int8)
+    A = rng.integers(-128, 128, (65536 * 64 + 70, 20), dtype=np.int8)
     W = rng.integers(-128, 128, (3, 20), dtype=np.int8)
     D.gemm_backend(SIMT)
     assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W))
