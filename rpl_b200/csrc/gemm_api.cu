@@ -67,7 +67,9 @@ static int launch_row_sums(const int8_t* X, int32_t* sums, uint64_t rows, uint64
 
 static int run_gemm(GemmProblem p, cudaStream_t st) {
     if (p.M == 0 || p.N == 0) return 0;
-    if (!p.A || !p.B || !p.out) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null pointer");
+    // An operand with no elements (K = 0) may legitimately be a null pointer.
+    if ((!p.A || !p.B) && p.K) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null input pointer");
+    if (!p.out) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null output pointer");
     if (p.ldo < p.N) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: output row stride %llu < N %llu",
                                  (unsigned long long)p.ldo, (unsigned long long)p.N);
     const int backend = g_backend.load(std::memory_order_relaxed);
