@@ -433,7 +433,8 @@ def run_ours(a):
 
     # DRAM traffic of the GEMM from the ncu capture at 16384 x 16384 x 8192
     # (profiles/gemm_i8_tc_kernel_8192cubed.md): 6.99 B per output element at K = 8192.
-    traffic = 6.99 * M * count if K == 8192 else None
+    gemm_launches_per_step = max(1, len(gemm_pairs) // max(a.steps, 1)) if a.overlap > 1 else 1
+    traffic = 6.99 * M * count / gemm_launches_per_step if K == 8192 else None
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
     line = {
@@ -449,7 +450,8 @@ def run_ours(a):
                          "per_rank_gemm_quant_step": per_rank},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by output elements)",
-                     "algorithmic_bytes": float(M * K + count * K + 4 * M * count), "kernel": "gemm_i8_tc_kernel",
+                     "algorithmic_bytes": float(M * K + count * K + 4 * M * count) / gemm_launches_per_step,
+                     "launches_per_step": gemm_launches_per_step, "kernel": "gemm_i8_tc_kernel",
                      "peak_note": "2 x bf16_tflops_sustained of %s (int8 dense = 2 x bf16 dense)" % peaks["source"],
                      "frac_of_nominal_4500": achieved / 4500.0},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
