@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--overlap", type=int, default=-1,
                     help="row blocks for pipelining the quantize pass under the GEMM (0 = sequential, "
                          "-1 = choose: pipelined when a rank's GEMM is short enough for the quantize pass to matter)")
-    ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 single-CTA tcgen05, 4 CTA-pair tcgen05)")
+    ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 tcgen05 128x256 tiles, 4 CTA pair, 5 256x256 tiles per CTA)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
 

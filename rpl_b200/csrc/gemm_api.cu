@@ -8,7 +8,7 @@ namespace rplb {
 
 int gemm_tcgen05_status(bool clear);     // gemm_i8_tcgen05.cu
 
-static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 single-CTA, 4 tcgen05 CTA pair
+static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA
 
 // Below this many multiply-accumulates the persistent tensor-core kernel has
 // no advantage over the dp4a kernel (one tile is 128 x 256 outputs).
@@ -117,7 +117,7 @@ using namespace rplb;
 extern "C" {
 
 int rplb_gemm_backend(int which) {
-    if (which < 0 || which > 4) return g_backend.load();
+    if (which < 0 || which > 5) return g_backend.load();
     return g_backend.exchange(which);
 }
 

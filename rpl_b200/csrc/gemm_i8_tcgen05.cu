@@ -593,6 +593,164 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
 }
 
+// --------------------------------------------------------------------------- the wide single-CTA kernel
+// One CTA computes a 256 x 256 output tile as two 128 x 256 accumulators that
+// share every W stage: per K step the CTA loads 256 rows of A and 256 rows of W
+// (64 KiB, three stages) and issues the MMAs of the upper and the lower half
+// against the same W tile.  Against the 128 x 256 kernel this moves a third
+// less data from L2 to the SM per output (512 instead of 768 rows per 256 x 256
+// outputs); the price is that both accumulators belong to one tile, so the
+// epilogue does not overlap the next tile's main loop.  At the board's power
+// cap what counts is energy per operation, not idle cycles.
+constexpr int WIDE_TILE_M = 256;
+constexpr int kWideStages = 3;
+constexpr uint32_t WIDE_A_BYTES = WIDE_TILE_M * TILE_K;   // 32 KiB
+constexpr uint32_t WIDE_B_BYTES = TILE_N * TILE_K;        // 32 KiB
+constexpr uint32_t WIDE_STAGE_BYTES = WIDE_A_BYTES + WIDE_B_BYTES;
+constexpr int WIDE_GROUP_M = 16;
+
+struct __align__(16) WideShared {
+    uint64_t full[kWideStages];
+    uint64_t empty[kWideStages];
+    uint64_t acc_full;               // MMA -> epilogue: both accumulators complete
+    uint64_t acc_empty;              // epilogue -> MMA: both accumulators drained
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    float w_scales[4 * TILE_N];
+    float bias[4 * TILE_N];
+};
+constexpr size_t WIDE_SMEM_BYTES = 1024 + (size_t)kWideStages * WIDE_STAGE_BYTES + sizeof(WideShared);
+
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    WideShared* sh = reinterpret_cast<WideShared*>(smem + (size_t)kWideStages * WIDE_STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWideStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+        mbar_init(&sh->acc_full, 1);
+        mbar_init(&sh->acc_empty, kEpilogueThreads / 32);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                uint32_t tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, &sh->abort_flag, status, TC_WAIT_EMPTY)) { ok = false; break; }
+                    uint8_t* a_dst = smem + (size_t)stage * WIDE_STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + WIDE_A_BYTES;
+                    mbar_expect_tx(&sh->full[stage], WIDE_STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tm * WIDE_TILE_M));
+                    tma_load_2d(b_dst, &map_w, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tn * TILE_N));
+                    if (++stage == kWideStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                if (!mbar_wait_bounded(&sh->acc_empty, acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) break;
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait_bounded(&sh->full[stage], phase, &sh->abort_flag, status, TC_WAIT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * WIDE_STAGE_BYTES);
+                    const uint64_t a_lo = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t a_hi = make_kmajor_sw128_desc(a_addr + 128 * TILE_K);     // rows 128..255 of the A stage
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + WIDE_A_BYTES);
+                    #pragma unroll
+                    for (int k = 0; k < TILE_K / MMA_K; k++) {
+                        const uint64_t adv = (uint64_t)(k * (MMA_K >> 4));
+                        const uint32_t accumulate = (kb | (uint32_t)k) != 0 ? 1u : 0u;
+                        tc_mma_i8(tmem_base, a_lo + adv, b_desc + adv, kIdescI8, accumulate);             // columns 0..255
+                        tc_mma_i8(tmem_base + TILE_N, a_hi + adv, b_desc + adv, kIdescI8, accumulate);    // columns 256..511
+                    }
+                    tc_commit(&sh->empty[stage]);
+                    if (++stage == kWideStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(&sh->acc_full);
+                acc_phase ^= 1;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- epilogue
+        const uint32_t quarter = (uint32_t)warp & 3u;
+        const int ew = warp - kEpilogueWarp0;
+        float* s_scales = sh->w_scales + ew * TILE_N;
+        float* s_bias = sh->bias + ew * TILE_N;
+        const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
+        const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
+        float absmax = 0.0f;
+        uint32_t acc_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint32_t tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M);
+            const uint64_t n0 = (uint64_t)tn * TILE_N;
+            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            bool ok = mbar_wait_bounded(&sh->acc_full, acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            #pragma unroll 1
+            for (int half = 0; half < 2; half++) {
+                const uint64_t m = (uint64_t)tm * WIDE_TILE_M + half * 128 + quarter * 32 + lane;
+                const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
+                #pragma unroll 1
+                for (int chunk = 0; chunk < TILE_N / 32; chunk++) {
+                    const uint64_t n_first = n0 + (uint64_t)chunk * 32;
+                    if (n_first >= p.N) break;
+                    uint32_t r[32];
+                    tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)half * TILE_N + (uint32_t)chunk * 32u, r);
+                    tc_wait_ld();
+                    store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->acc_empty);
+            acc_phase ^= 1;
+        }
+        if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
+    }
+
+    // ----------------------------------------------------------------- teardown
+    if (sh->abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 // --------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -729,7 +887,21 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const Ge
     return launched("gemm_i8_tc_pair_kernel");
 }
 
-// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = CTA pair per 256 x 256 tile.
+template <int MODE>
+static int launch_tc_wide(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t num_kb,
+                          int* status_dev, unsigned int sms, cudaStream_t st) {
+    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)WIDE_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_wide_kernel)")) return rc;
+    const uint32_t tiles_m = (uint32_t)((p.M + WIDE_TILE_M - 1) / WIDE_TILE_M);
+    const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
+    const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
+    const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
+    gemm_i8_tc_wide_kernel<MODE><<<grid, TC_THREADS, WIDE_SMEM_BYTES, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    return launched("gemm_i8_tc_wide_kernel");
+}
+
+// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = CTA pair per 256 x 256 tile,
+// 3 = one CTA per 256 x 256 tile (two accumulators sharing each W stage).
 int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W");
@@ -755,6 +927,17 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         variant = (pair_tiles >= sms / 2 && macs < 1.1e12) ? 2 : 1;
     }
     CUtensorMap ma, mw;
+    if (variant == 3) {
+        if (int rc = make_map(&ma, p.A, p.M, p.K, WIDE_TILE_M)) return rc;
+        if (int rc = make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
+        switch (p.mode) {
+            case EPI_RAW_I32:     return launch_tc_wide<EPI_RAW_I32>(ma, mw, p, num_kb, status_dev, sms, st);
+            case EPI_REQUANT_I32: return launch_tc_wide<EPI_REQUANT_I32>(ma, mw, p, num_kb, status_dev, sms, st);
+            case EPI_DEQUANT_F32: return launch_tc_wide<EPI_DEQUANT_F32>(ma, mw, p, num_kb, status_dev, sms, st);
+            case EPI_DEQUANT_I8:  return launch_tc_wide<EPI_DEQUANT_I8>(ma, mw, p, num_kb, status_dev, sms, st);
+        }
+        return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
+    }
     if (variant == 2) {
         if (int rc = make_map(&ma, p.A, p.M, p.K, 128)) return rc;
         if (int rc = make_map(&mw, p.B, p.N, p.K, 128)) return rc;

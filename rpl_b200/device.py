@@ -35,7 +35,8 @@ def launch_count():
 
 
 def gemm_backend(which):
-    """0 automatic, 1 dp4a, 2 tcgen05 (3 = single-CTA tiles, 4 = CTA-pair tiles); returns the previous setting."""
+    """0 automatic, 1 dp4a, 2 tcgen05 (3 = 128x256 tiles, 4 = CTA-pair 256x256 tiles, 5 = 256x256 tiles per CTA);
+    returns the previous setting."""
     return int(capi.load().rplb_gemm_backend(int(which)))
 
 

@@ -9,7 +9,7 @@ from conftest import bits
 
 pytestmark = pytest.mark.gpu
 
-SIMT, TC, TC_SINGLE, TC_PAIR = 1, 2, 3, 4      # rplb_gemm_backend codes
+SIMT, TC, TC_SINGLE, TC_PAIR, TC_WIDE = 1, 2, 3, 4, 5      # rplb_gemm_backend codes
 
 
 def same(a, b):
@@ -70,7 +70,7 @@ def test_tcgen05_raw_and_bias(cuda, lib, port, backend, mnk):
     W = rng.integers(-128, 128, (N, K), dtype=np.int8)
     b = rng.integers(-128, 128, N, dtype=np.int8)
     want = port.linear(A, W)
-    for which in (TC_SINGLE, TC_PAIR, TC):
+    for which in (TC_SINGLE, TC_PAIR, TC_WIDE, TC):
         D.gemm_backend(which)
         got = host(D.linear_i8(dev(A, cuda), dev(W, cuda)))
         torch.cuda.synchronize()
@@ -82,7 +82,7 @@ def test_tcgen05_raw_and_bias(cuda, lib, port, backend, mnk):
 
 
 @pytest.mark.parametrize("mnk", [(64, 64, 64), (130, 300, 784), (512, 512, 512), (33, 77, 19), (5, 3, 1)])
-@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR, TC_WIDE])
 def test_requant_epilogue(cuda, lib, port, backend, mnk, which):
     D = backend
     M, N, K = mnk
@@ -100,7 +100,7 @@ def test_requant_epilogue(cuda, lib, port, backend, mnk, which):
 
 
 @pytest.mark.parametrize("mnk", [(128, 256, 128), (37, 23, 144), (130, 300, 784), (256, 10, 128), (512, 512, 512)])
-@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR, TC_WIDE])
 @pytest.mark.parametrize("relu", [False, True])
 def test_fused_dequant_epilogue(cuda, lib, port, backend, mnk, which, relu):
     D = backend
@@ -131,7 +131,7 @@ def test_fused_epilogue_writes_a_column_block_in_place(cuda, lib, port, backend)
     ws = ((rng.random(N) + 0.5) * 1e-4).astype(np.float32)
     want = port.linear_dequant(A, W, 0.01, ws, None, False)
     a_dev = dev(np.array([0.01], np.float32), cuda)
-    for which in (SIMT, TC_SINGLE, TC_PAIR):
+    for which in (SIMT, TC_SINGLE, TC_PAIR, TC_WIDE):
         D.gemm_backend(which)
         full = torch.full((M, NT), -7.0, device=cuda)
         D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda), out=full[:, 256:512])
@@ -151,7 +151,7 @@ def test_config1_512_cubed_end_to_end(cuda, lib, port, backend):
     wqa, sa = port.quantize_symmetric(A)
     wqb, sb = port.quantize_symmetric(Bt)
     assert same(host(qa), wqa) and same(host(qb), wqb)
-    for which in (SIMT, TC_SINGLE, TC_PAIR):
+    for which in (SIMT, TC_SINGLE, TC_PAIR, TC_WIDE):
         D.gemm_backend(which)
         assert same(host(D.linear_i8(qa, qb)), port.linear(wqa, wqb))
         Bkn = np.ascontiguousarray(wqb.T)
@@ -173,6 +173,8 @@ def test_tcgen05_matches_dp4a_at_projection_size(cuda, lib, backend):
     D.gemm_backend(TC_PAIR)
     c_tc = D.linear_i8(A, W)
     D.gemm_backend(TC_SINGLE)
+    assert torch.equal(D.linear_i8(A, W), c_tc)
+    D.gemm_backend(TC_WIDE)
     assert torch.equal(D.linear_i8(A, W), c_tc)
     D.gemm_backend(SIMT)
     c_simt = D.linear_i8(A, W)
@@ -200,7 +202,7 @@ def test_sampled_tiles_vs_checker_at_projection_size(cuda, lib, port, backend):
 
 
 @pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (64, 40, 16)])
-@pytest.mark.parametrize("which", [TC_SINGLE, TC_PAIR])
+@pytest.mark.parametrize("which", [TC_SINGLE, TC_PAIR, TC_WIDE])
 def test_zero_points_on_the_tensor_core_path(cuda, lib, port, backend, mnk, which):
     """gemm_int8 with za, zb != 0: the tensor-core kernels correct the plain product
     with row sums of A and column sums of B in the epilogue."""
@@ -216,7 +218,7 @@ def test_zero_points_on_the_tensor_core_path(cuda, lib, port, backend, mnk, whic
 
 
 @pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (65, 10, 128)])
-@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR, TC_WIDE])
 def test_epilogue_reports_absmax_for_the_next_layer(cuda, lib, port, backend, mnk, which):
     D = backend
     M, N, K = mnk
@@ -238,7 +240,7 @@ def test_epilogue_reports_absmax_for_the_next_layer(cuda, lib, port, backend, mn
 
 
 @pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (65, 10, 128), (256, 256, 256)])
-@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR])
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR, TC_WIDE])
 def test_int8_output_with_a_static_scale(cuda, lib, port, backend, mnk, which):
     D = backend
     M, N, K = mnk
