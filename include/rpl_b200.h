@@ -351,6 +351,19 @@ void    linear_int8_dequant(const QuantizedTensor* x, const PerChannelQuantizedT
                             float* out, uint32_t batch_size, uint32_t in_features, uint32_t out_features,
                             bool relu);
 
+/* A quantized Linear layer, the INT8 counterpart of linear_create /
+ * linear_forward / linear_free (include/rpl.h:230-232, src/rpl_nn.c:23-82):
+ * y = x . W^T + b with W [out_features, in_features].  create quantizes the fp32
+ * weight per output row (tensor_quantize_per_channel) and keeps it, its scales
+ * and the fp32 bias (may be NULL) in device memory; forward quantizes the
+ * activation per tensor (symmetric) and runs the INT8 GEMM with the fused
+ * dequantize + bias (+ ReLU) epilogue.  The result is a new Tensor
+ * [rows, out_features], in device memory if the input was, else in host memory. */
+typedef struct QuantizedLinear QuantizedLinear;
+QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bias);
+Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bool relu);
+void    quantized_linear_free(QuantizedLinear* layer);
+
 /* Quantized weights on disk, in the framing of the reference's fp32 checkpoint
  * writer (checkpoint_save_model, src/rpl_training.c:915-944; the reference has
  * no loader and no int8 format): header {count, tag "INT8", 0.0f}, then per

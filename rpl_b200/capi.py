@@ -136,6 +136,9 @@ SIGNATURES = {
     "tensor_download": (_TP, [_TP]),
     "linear_int8_dequant": (None, [_QP, _PP, _vp, _vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_bool]),
     "tensor_dequantize_per_channel": (_TP, [_PP]),
+    "quantized_linear_create": (_vp, [_TP, _TP]),
+    "quantized_linear_forward": (_TP, [_vp, _TP, C.c_bool]),
+    "quantized_linear_free": (None, [_vp]),
     "quantized_weights_save": (C.c_int, [C.c_char_p, C.POINTER(_PP), C.c_uint32]),
     "quantized_weights_load": (C.POINTER(_PP), [C.c_char_p, C.POINTER(C.c_uint32), C.c_bool]),
 }

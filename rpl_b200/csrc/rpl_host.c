@@ -635,3 +635,91 @@ PerChannelQuantizedTensor** quantized_weights_load(const char* path, uint32_t* n
     *num_tensors = n_t;
     return out;
 }
+
+/* ------------------------------------------------------------------------
+ * A quantized Linear layer: what linear_forward (src/rpl_nn.c:55-77) computes,
+ * x . W^T + b with W [out_features, in_features], on the INT8 path.  The
+ * weights are quantized per output row once, at creation, and stay in device
+ * memory with their scales and the fp32 bias; forward quantizes the
+ * activation per tensor (tensor_quantize_int8_symmetric's arithmetic) and runs
+ * the INT8 GEMM with the fused dequantize + bias (+ ReLU) epilogue.
+ * ---------------------------------------------------------------------- */
+struct QuantizedLinear {
+    PerChannelQuantizedTensor* weight;   /* device-resident int8 rows, scales, zero points */
+    float*   bias;                       /* device, out_features floats, or NULL */
+    uint32_t in_features;
+    uint32_t out_features;
+    int8_t*  act;                        /* device buffer for the quantized activation */
+    size_t   act_capacity;
+    rplb_qparams* act_params;            /* device */
+};
+
+void quantized_linear_free(QuantizedLinear* layer) {
+    if (!layer) return;
+    per_channel_quantized_tensor_free(layer->weight);
+    rplb_free(layer->bias);
+    rplb_free(layer->act);
+    rplb_free(layer->act_params);
+    free(layer);
+}
+
+QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bias) {
+    if (!weight || weight->dims != 2) return NULL;
+    t_last_error = 0;
+    const char* who = "quantized_linear_create";
+    QuantizedLinear* layer = (QuantizedLinear*)calloc(1, sizeof(QuantizedLinear));
+    if (!layer) return NULL;
+    layer->out_features = weight->shape[0];
+    layer->in_features = weight->shape[1];
+    /* Quantize on the device and keep the result there: a device-resident input
+     * makes tensor_quantize_per_channel return device-resident blocks. */
+    Tensor* wdev = on_device(weight->data) ? NULL : tensor_upload(weight);
+    layer->weight = tensor_quantize_per_channel(wdev ? wdev : weight, 0);
+    tensor_free(wdev);
+    void* params = NULL;
+    if (!layer->weight || report(rplb_malloc(&params, sizeof(rplb_qparams)), who) != 0) { quantized_linear_free(layer); return NULL; }
+    layer->act_params = (rplb_qparams*)params;
+    if (bias) {
+        void* b = NULL;
+        if (bias->size != layer->out_features || report(rplb_malloc(&b, (size_t)bias->size * 4), who) != 0 ||
+            report(rplb_copy(b, bias->data, (size_t)bias->size * 4, NULL), who) != 0 || finish(who) != 0) {
+            rplb_free(b);
+            quantized_linear_free(layer);
+            return NULL;
+        }
+        layer->bias = (float*)b;
+    }
+    return layer;
+}
+
+Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bool relu) {
+    if (!layer || !input || input->dims < 1 || input->size % layer->in_features != 0) return NULL;
+    t_last_error = 0;
+    const char* who = "quantized_linear_forward";
+    const size_t K = layer->in_features, N = layer->out_features, M = input->size / K;
+    const int dev_in = on_device(input->data);
+    uint32_t out_shape[2] = {(uint32_t)M, (uint32_t)N};                      /* src/rpl_nn.c:57 */
+    Tensor* out = dev_in ? tensor_create_device(2, out_shape) : tensor_create(2, out_shape, false);
+    if (!out) return NULL;
+    if (layer->act_capacity < M * K) {
+        rplb_stream_sync(NULL);
+        rplb_free(layer->act);
+        layer->act = NULL;
+        layer->act_capacity = 0;
+        void* a = NULL;
+        if (report(rplb_malloc(&a, M * K), who) != 0) { tensor_free(out); return NULL; }
+        layer->act = (int8_t*)a;
+        layer->act_capacity = M * K;
+    }
+    const float* x = (const float*)to_device(0, input->data, M * K * 4);
+    float* o = dev_in ? out->data : (float*)stage(3, M * N * 4);
+    if ((M * K && !x) || !o) { tensor_free(out); return NULL; }
+    if (report(rplb_quantize_symmetric_f32_i8(x, layer->act, M * K, layer->act_params, NULL), who) != 0 ||
+        report(rplb_linear_i8_dequant_f32(layer->act, layer->weight->data, o, M, K, N, N, &layer->act_params->scale_sym,
+                                          layer->weight->scales, layer->bias, relu ? 1 : 0, NULL), who) != 0 ||
+        (!dev_in && report(rplb_copy(out->data, o, M * N * 4, NULL), who) != 0) || finish(who) != 0) {
+        tensor_free(out);
+        return NULL;
+    }
+    return out;
+}

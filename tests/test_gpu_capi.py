@@ -194,3 +194,42 @@ def test_calibrator_and_model_quantize(cuda, lib, port):
     assert same(read_host(r.contents.data, (4,), np.float32), port.relu(np.array([-1.0, 0.5, -0.0, 3.0], np.float32)))
     for t in params + [r]:
         lib.tensor_free(t)
+
+
+def test_quantized_linear_layers_chain_like_the_mlp(cuda, lib, port):
+    """quantized_linear_create / _forward (the INT8 counterpart of linear_create /
+    linear_forward): a 784 -> 128 -> 10 MLP on host tensors and on device tensors."""
+    rng = np.random.default_rng(31)
+    X = rng.random((300, 784), dtype=np.float32)
+    W1 = (rng.standard_normal((128, 784)) * 0.05).astype(np.float32)
+    W2 = (rng.standard_normal((10, 128)) * 0.05).astype(np.float32)
+    b1 = (rng.standard_normal(128) * 0.05).astype(np.float32)
+    tw1, tw2, tb1, tx = (host_tensor(lib, a) for a in (W1, W2, b1, X))
+    l1 = lib.quantized_linear_create(tw1, tb1)
+    l2 = lib.quantized_linear_create(tw2, None)
+    assert l1 and l2
+
+    w1q, w1s, _ = port.quantize_per_channel(W1, 128)
+    w2q, w2s, _ = port.quantize_per_channel(W2, 10)
+    xq, xs = port.quantize_symmetric(X)
+    h_want = port.linear_dequant(xq, w1q, xs, w1s, b1, relu=True)
+    hq, hs = port.quantize_symmetric(h_want)
+    y_want = port.linear_dequant(hq, w2q, hs, w2s, None, relu=False)
+
+    h = lib.quantized_linear_forward(l1, tx, True)
+    assert h and list(h.contents.shape[:2]) == [300, 128] and lib.rplb_pointer_kind(h.contents.data) == 0
+    assert same(read_host(h.contents.data, (300, 128), np.float32), h_want)
+    y = lib.quantized_linear_forward(l2, h, False)
+    assert same(read_host(y.contents.data, (300, 10), np.float32), y_want)
+
+    xd = lib.tensor_upload(tx)                         # same chain with device-resident activations
+    hd = lib.quantized_linear_forward(l1, xd, True)
+    yd = lib.quantized_linear_forward(l2, hd, False)
+    assert yd.contents.device == 1 and lib.rplb_pointer_kind(yd.contents.data) == 2
+    yh = lib.tensor_download(yd)
+    assert same(read_host(yh.contents.data, (300, 10), np.float32), y_want)
+    assert lib.rpl_cuda_last_error() == 0
+    for t in (h, y, xd, hd, yd, yh, tw1, tw2, tb1, tx):
+        lib.tensor_free(t)
+    lib.quantized_linear_free(l1)
+    lib.quantized_linear_free(l2)
