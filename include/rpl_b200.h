@@ -269,7 +269,7 @@ int  rplb_kernel_status(int clear);
  * 1 = dp4a kernel, 2 = tcgen05 kernel (RPLB_E_UNSUPPORTED if the shape does
  * not fit it), 3 = tcgen05 with one CTA per 128x256 tile, 4 = tcgen05 with a
  * CTA pair (cta_group::2) per 256x256 tile, 5 = tcgen05 with one CTA per
- * 256x256 tile (two accumulators); 2 picks among 3, 4 and 5 by size.
+ * 256x256 tile (two accumulators); 2 picks between 3 and 4 by size.
  * Returns the previous setting.  All of them are CUDA kernels. */
 int  rplb_gemm_backend(int which);
 

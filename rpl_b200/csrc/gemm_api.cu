@@ -76,11 +76,13 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
     if (backend == 1) return gemm_simt(p, st);
 
     GemmProblem q = p;
-    const bool big = p.M * p.N * (p.K ? p.K : 1) >= kTcMinMacs;
-    const bool want_tc = (backend >= 2 || big) && p.K && p.K % 16 == 0;
+    const bool big = (double)p.M * (double)p.N * (double)(p.K ? p.K : 1) >= (double)kTcMinMacs;
+    // What the tensor-core kernel will need once B is K-contiguous: K % 16 == 0 and
+    // 16-byte aligned operands (the transposed copy in scratch is aligned by construction).
+    const bool want_tc = (backend >= 2 || big) && p.K && p.K % 16 == 0 && (((uintptr_t)p.A & 15) == 0) &&
+                         (p.b_is_kn || (((uintptr_t)p.B & 15) == 0));
     const bool zero_points = p.mode == EPI_REQUANT_I32 && (p.za || p.zb);
-    if (want_tc && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535 &&
-        p.M <= 0x7fffffffull * 8 && p.N <= 0x7fffffffull * 8) {
+    if (want_tc && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535) {
         // Library scratch: [ B as [N,K] | row sums of A | column sums of B ].
         const size_t bt_bytes = p.b_is_kn ? (((size_t)(p.K * p.N) + 255) & ~(size_t)255) : 0;
         const size_t rs_bytes = zero_points ? (((size_t)p.M * 4 + 255) & ~(size_t)255) : 0;
