@@ -264,6 +264,12 @@ int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
  * 4 accumulator-ready).  Readable at any time; clear != 0 resets it. */
 int  rplb_kernel_status(int clear);
 
+/* Exercises the give-up path of the tensor-core kernels without a GEMM: one
+ * warp waits about a millisecond on a barrier that nothing signals, gives up,
+ * records its code and returns.  0 = the kernel returned, the status word held
+ * the expected code and has been cleared.  Never blocks longer than the limit. */
+int  rplb_selftest_bounded_wait(void* stream);
+
 /* Which contraction kernel the three calls above use: 0 = automatic (tcgen05
  * tensor-core kernel when the shape allows it, else the dp4a kernel),
  * 1 = dp4a kernel, 2 = tcgen05 kernel (RPLB_E_UNSUPPORTED if the shape does

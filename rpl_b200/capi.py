@@ -106,6 +106,7 @@ SIGNATURES = {
     "rplb_linear_i8_requant_i8": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _i, _vp]),
     "rplb_gemm_backend": (C.c_int, [C.c_int]),
     "rplb_kernel_status": (C.c_int, [C.c_int]),
+    "rplb_selftest_bounded_wait": ("rc", [_vp]),
     "rplb_shard_range": ("rc", [_u64, C.c_int, C.c_int, _u64, C.POINTER(_u64), C.POINTER(_u64)]),
     # reference-named layer
     "tensor_create": (_TP, [C.c_uint32, C.POINTER(C.c_uint32), C.c_bool]),

@@ -7,6 +7,7 @@
 namespace rplb {
 
 int gemm_tcgen05_status(bool clear);     // gemm_i8_tcgen05.cu
+int bounded_wait_selftest(cudaStream_t st);
 
 static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA
 
@@ -124,6 +125,8 @@ int rplb_gemm_backend(int which) {
 }
 
 int rplb_kernel_status(int clear) { return gemm_tcgen05_status(clear != 0); }
+
+int rplb_selftest_bounded_wait(void* stream) { return bounded_wait_selftest(as_stream(stream)); }
 
 int rplb_linear_i8_i32(const int8_t* x, const int8_t* w, const int8_t* bias, int32_t* out,
                        uint64_t M, uint64_t K, uint64_t N, void* stream) {

@@ -58,7 +58,7 @@ struct __align__(16) TcShared {
 constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)kStages * STAGE_BYTES + sizeof(TcShared);
 
 // Status codes written to the status word when a wait gives up.
-enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4 };
+enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4, TC_WAIT_SELFTEST = 99 };
 
 // --------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,14 +84,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Waits for the phase with the given parity.  Gives up after about a second
 // (or as soon as another role has given up) and returns false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+constexpr long long kWaitLimitCycles = 2000000000LL;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                  long long limit = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > 2000000000LL) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -751,6 +754,27 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
 }
 
+// --------------------------------------------------------------------------- self-test of the bounded wait
+// One warp waits, with a limit of about a millisecond, on an mbarrier that
+// nothing ever arrives on.  The wait must give up, record its code in the
+// status word and let the kernel return normally; result[0] = 1 when
+// mbar_wait_bounded returned false, result[1] = the abort flag it raised.
+__global__ void bounded_wait_selftest_kernel(int* status, int* result, long long limit_cycles) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait_bounded(&bar, 0, &abort_flag, status, TC_WAIT_SELFTEST, limit_cycles);
+        result[0] = ok ? 0 : 1;
+        result[1] = abort_flag;
+    }
+}
+
 // --------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -816,6 +840,34 @@ static int* kernel_status_word() {
         }
     });
     return word;
+}
+
+// Runs the kernel above and checks that the give-up path works end to end:
+// the kernel returns, the status word carries the code, and clearing it leaves
+// the library usable.  Returns 0 when everything behaved as designed.
+int bounded_wait_selftest(cudaStream_t st) {
+    int* status_host = kernel_status_word();
+    if (!status_host) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
+    if (*reinterpret_cast<volatile int*>(status_host) != 0)
+        return fail(RPLB_E_KERNEL, "status word not clear before the self-test (%d)", *status_host);
+    int* status_dev = nullptr;
+    if (int rc = cuda_ok(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0), "cudaHostGetDevicePointer")) return rc;
+    int* result = nullptr;
+    if (int rc = cuda_ok(cudaMalloc((void**)&result, 2 * sizeof(int)), "cudaMalloc(selftest)")) return rc;
+    cudaMemsetAsync(result, 0xff, 2 * sizeof(int), st);
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(status_dev, result, 2000000LL);
+    int rc = launched("bounded_wait_selftest_kernel");
+    int host_result[2] = {-1, -1};
+    if (!rc) rc = cuda_ok(cudaMemcpyAsync(host_result, result, sizeof(host_result), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(selftest)");
+    if (!rc) rc = cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize(selftest)");
+    cudaFree(result);
+    if (rc) return rc;
+    const int code = *reinterpret_cast<volatile int*>(status_host);
+    *reinterpret_cast<volatile int*>(status_host) = 0;
+    if (host_result[0] != 1 || host_result[1] != 1 || code != TC_WAIT_SELFTEST)
+        return fail(RPLB_E_KERNEL, "bounded wait self-test: gave_up=%d abort=%d status=%d (expected 1, 1, %d)",
+                    host_result[0], host_result[1], code, (int)TC_WAIT_SELFTEST);
+    return 0;
 }
 
 int gemm_tcgen05_status(bool clear) {

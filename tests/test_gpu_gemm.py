@@ -275,3 +275,20 @@ def test_empty_and_degenerate_shapes(cuda, lib, port, backend):
     W = rng.integers(-128, 128, (3, 20), dtype=np.int8)
     D.gemm_backend(SIMT)
     assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W))
+
+
+def test_bounded_wait_gives_up_and_reports(cuda, lib, port, backend):
+    """A wait on a barrier that nothing signals must end by itself (about a
+    millisecond here), leave its code in the status word, and leave the library
+    usable: the next GEMM runs and is correct."""
+    import ctypes as C
+    from rpl_b200 import capi
+    D = backend
+    assert D.kernel_status(True) == 0
+    capi.call("rplb_selftest_bounded_wait", C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert D.kernel_status(False) == 0                  # the self-test clears what it provoked
+    rng = np.random.default_rng(1)
+    A = rng.integers(-128, 128, (128, 256), dtype=np.int8)
+    W = rng.integers(-128, 128, (256, 256), dtype=np.int8)
+    D.gemm_backend(TC_SINGLE)
+    assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W))
