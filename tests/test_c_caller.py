@@ -50,3 +50,35 @@ def test_c_caller_results_match_plain_c_loops(tmp_path, lib, cuda, use_reference
     exe = _build(tmp_path, lib, use_reference_header)
     out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "drop_in_check: OK" in out.stdout, out.stdout + out.stderr
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(os.path.dirname(REF_INCLUDE), "src", "rpl_nn.c")),
+                    reason="reference tree absent")
+def test_combined_library_keeps_the_rest_of_the_reference(tmp_path, lib):
+    """The linking recipe of INTEGRATION.md: the reference's own objects (its INT8
+    symbols weakened) next to this library's objects give one library in which the
+    fp32 layers are the reference's and the INT8 path is this one."""
+    import ctypes as C
+    import glob
+    from rpl_b200 import build
+    ref = os.path.dirname(REF_INCLUDE)
+    objs = []
+    for src in sorted(glob.glob(os.path.join(ref, "src", "*.c"))):
+        name = os.path.basename(src)[:-2]
+        if name == "rpi_ml":                      # not part of the reference's own build
+            continue
+        o = str(tmp_path / (name + ".o"))
+        subprocess.run(["/usr/bin/gcc", "-O1", "-fopenmp", "-fPIC", "-w", "-I", REF_INCLUDE, "-c", src, "-o", o], check=True)
+        if name in ("rpl_core", "ops_extended", "rpl_quantization"):
+            subprocess.run(["objcopy", "--weaken", o], check=True)
+        objs.append(o)
+    ours = sorted(glob.glob(os.path.join(build.OBJ_DIR, "*.o")))
+    out = str(tmp_path / "librpl_full.so")
+    subprocess.run([build._nvcc(), "-shared", "-o", out] + objs + ours + ["-cudart", "static", "-Xcompiler", "-fopenmp", "-lm"],
+                   check=True, capture_output=True)
+    L = C.CDLL(out)
+    for name in ("tensor_gemm", "linear_forward", "optimizer_adam_create", "rplb_minmax_f32", "quantized_linear_forward"):
+        assert hasattr(L, name), name
+    # the INT8 entry point is this library's: it can report a CUDA error code
+    L.rpl_cuda_last_error.restype = C.c_int
+    assert L.rpl_cuda_last_error() == 0
