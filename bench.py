@@ -220,13 +220,13 @@ def event_ms(pairs):
     return [a.elapsed_time(b) for a, b in pairs]
 
 
-def quantize_sweep(torch, D, dev, peaks):
-    """Quantize / dequantize GB/s on 2^26 fp32 elements (256 MiB > L2), rows of 4096."""
-    n = 1 << 26
+def quantize_sweep_one(torch, D, dev, peaks, n):
+    """Quantize / dequantize GB/s on n fp32 elements, rows of 4096: N(0,3) with outliers at +/-50."""
     g = torch.Generator(device=dev)
     g.manual_seed(0x5EED0040)
     x = torch.randn(n, device=dev, generator=g) * 3.0
     x[::1009] = 50.0
+    x[5::2003] = -50.0
     q = torch.empty(n, dtype=torch.int8, device=dev)
     params = torch.empty(8, dtype=torch.float32, device=dev)
     back = torch.empty(n, dtype=torch.float32, device=dev)
@@ -234,7 +234,7 @@ def quantize_sweep(torch, D, dev, peaks):
     cases = [
         ("quantize_explicit_scale", 5.0, lambda: D.quantize(x, 0.3937, 0, out=q)),
         ("quantize_per_tensor_symmetric", 9.0, lambda: D.quantize_symmetric(x, out=q, params=params)),
-        ("minmax", 4.0, lambda: D.minmax(x)),
+        ("minmax", 4.0, lambda: D.minmax(x, params=params)),
         ("quantize_per_channel_rows4096", 5.0, lambda: D.quantize_per_channel(x2, out=q.view(-1, 4096))),
         ("dequantize", 5.0, lambda: D.dequantize(q, 0.3937, 0, out=back)),
     ]
@@ -243,7 +243,7 @@ def quantize_sweep(torch, D, dev, peaks):
     for name, bytes_per_elem, fn in cases:
         for _ in range(3):
             fn()
-        # 20 launches between one pair of events (a kernel here lasts ~50 us: an event
+        # 20 launches between one pair of events (a kernel here can last ~50 us: an event
         # pair around every launch would time the launch gap as well), 5 such groups.
         reps, groups = 20, 5
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)]
@@ -260,6 +260,20 @@ def quantize_sweep(torch, D, dev, peaks):
         gbs = bytes_per_elem * n / (med * 1e-3) / 1e9
         res[name] = {"ms": med, "gbs": gbs, "bytes_per_elem": bytes_per_elem, "frac": gbs / peaks["hbm_gbs"]}
     res["launches"] = launches
+    return res
+
+
+def quantize_sweep(torch, D, dev, peaks):
+    """The memory-bound sweep: 2^26 elements (256 MiB, larger than L2) is the quoted
+    size; 2^20 (fits in L2: launch- and L2-bound) and 2^30 (4 GiB) ride along."""
+    res = quantize_sweep_one(torch, D, dev, peaks, 1 << 26)
+    res["other_sizes"] = {}
+    for n in (1 << 20, 1 << 30):
+        r = quantize_sweep_one(torch, D, dev, peaks, n)
+        res["other_sizes"][str(n)] = {k: {"ms": v["ms"], "gbs": v["gbs"], "frac": v["frac"]} for k, v in r.items()
+                                      if isinstance(v, dict)}
+        res["launches"] += r["launches"]
+        torch.cuda.empty_cache()
     return res
 
 
