@@ -236,6 +236,11 @@ def quantize_sweep_one(torch, D, dev, peaks, n):
         ("quantize_per_tensor_symmetric", 9.0, lambda: D.quantize_symmetric(x, out=q, params=params)),
         ("minmax", 4.0, lambda: D.minmax(x, params=params)),
         ("quantize_per_channel_rows4096", 5.0, lambda: D.quantize_per_channel(x2, out=q.view(-1, 4096))),
+        # the other reading of "rows of 4096 channels": 4096 channels of n/4096 elements each.  A channel is
+        # read twice by its CTA; the second read comes from L2 while the ~1184 channels in flight fit there
+        # (5 B/element of HBM traffic), otherwise both passes go to HBM (9 B/element).
+        ("quantize_per_channel_4096_channels", 5.0 if (n // 4096) * 4 * 1184 <= 100e6 else 9.0,
+         lambda: D.quantize_per_channel(x.view(4096, -1), out=q.view(4096, -1))),
         ("dequantize", 5.0, lambda: D.dequantize(q, 0.3937, 0, out=back)),
     ]
     res = {"elements": n, "unit": "GB/s", "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]}
