@@ -2,7 +2,16 @@
 //
 // C[m,n] = sum_k A[m,k] * W[n,k], A [M,K] and W [N,K] both K-contiguous
 // (the layout of linear_int8, src/rpl_quantization.c:340-343), followed by one
-// of the three epilogues of the path.
+// of the epilogues of the path: raw int32 (+ int8 bias), gemm_int8's
+// requantization (with zero-point correction from row / column sums), the fused
+// fp32 dequantize + bias + ReLU (optionally reporting max |out|), or that value
+// quantized straight to int8.
+//
+// Three kernels share the helpers in this file and differ in how a tile is
+// spread over SMs: gemm_i8_tc_kernel (one CTA, 128 x 256 tile, described below;
+// the default for long GEMMs), gemm_i8_tc_pair_kernel (two CTAs of a cluster on
+// a 256 x 256 tile with cta_group::2; the default for short GEMMs) and
+// gemm_i8_tc_wide_kernel (one CTA, 256 x 256 tile in two accumulators).
 //
 // One persistent CTA per SM, 192 threads in three roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor.2d loads of a 128 x 128-byte
