@@ -423,26 +423,38 @@ def run_ours(a):
     # ---- end to end through host buffers ----
     e2e = None
     if not a.no_e2e:
-        xh = torch.empty((M, K), dtype=torch.float32, pin_memory=True)
-        oh = torch.empty((M, count), dtype=torch.float32, pin_memory=True)
-        xh.copy_(A)
-        torch.cuda.synchronize()
-        layer.forward_host(xh, oh)
-        esteps = max(1, min(a.steps, 5))
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(esteps):
-            layer.forward_host(xh, oh)
-        s1.record()
-        barrier()
-        te = torch.tensor([s0.elapsed_time(s1) / esteps], device=dev)
+        xh = oh = None
+        try:
+            xh = torch.empty((M, K), dtype=torch.float32, pin_memory=True)
+            oh = torch.empty((M, count), dtype=torch.float32, pin_memory=True)
+            have = 1
+        except RuntimeError:
+            have = 0
+        agreed = torch.tensor([have], device=dev)
         if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        same = bool(torch.equal(oh[:256].to(dev), out[:256]))
-        e2e = {"value": ops_total / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(te.item()),
-               "steps": esteps, "h2d_bytes_per_step": int(M * K * 4) * world, "d2h_bytes_per_step": int(M * N * 4),
-               "api": "ShardedQuantizedLinear.forward_host (page-locked host buffers)", "matches_device_run": same}
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)          # all ranks take the same branch
+        if int(agreed.item()) == 0:
+            e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "error": "page-locked host buffers (%.1f GiB per rank) could not be allocated" % ((M * K + M * count) * 4 / 2**30)}
+        else:
+            xh.copy_(A)
+            torch.cuda.synchronize()
+            layer.forward_host(xh, oh)
+            esteps = max(1, min(a.steps, 5))
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(esteps):
+                layer.forward_host(xh, oh)
+            s1.record()
+            barrier()
+            te = torch.tensor([s0.elapsed_time(s1) / esteps], device=dev)
+            if world > 1:
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            same = bool(torch.equal(oh[:256].to(dev), out[:256]))
+            e2e = {"value": ops_total / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(te.item()),
+                   "steps": esteps, "h2d_bytes_per_step": int(M * K * 4) * world, "d2h_bytes_per_step": int(M * N * 4),
+                   "api": "ShardedQuantizedLinear.forward_host (page-locked host buffers)", "matches_device_run": same}
         del xh, oh
 
     if rank != 0:
