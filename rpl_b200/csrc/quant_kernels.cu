@@ -25,6 +25,13 @@ static inline unsigned int stream_grid(uint64_t work_items, uint64_t items_per_c
     return (unsigned int)(need < cap ? need : cap);
 }
 
+// One CTA per `items_per_cta` items (the kernels' grid-stride loops then run once).
+static inline unsigned int one_shot_grid(uint64_t work_items, uint64_t items_per_cta) {
+    uint64_t need = (work_items + items_per_cta - 1) / items_per_cta;
+    if (need < 1) need = 1;
+    return (unsigned int)(need < 0x7fffffffull ? need : 0x7fffffffull);
+}
+
 // ---------------------------------------------------------------------------
 // min/max  (src/ops_extended.c:52-61, src/rpl_quantization.c:79-85)
 // ---------------------------------------------------------------------------
@@ -170,7 +177,12 @@ static int launch_quantize(const float* x, int8_t* q, uint64_t n, float scale, i
     const bool vec = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
     uint64_t nquads = vec ? n / 4 : 0;
     if (nquads) {
-        unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+        // One CTA per step rather than a resident grid striding over the tensor: measured
+        // 3-4 % faster for the forward walk (6531 vs 6302 GB/s at 2^26 elements, 6853 vs 6581 at 2^30).
+        // The reversed walk after a min/max pass keeps the resident grid while the tensor is within a
+        // few L2 sizes, where it re-uses more of what that pass left in L2 (6307 vs 6114 GB/s at 2^26).
+        unsigned int grid = one_shot_grid(nquads, (uint64_t)kThreads * kUnroll);
+        if (reverse && nquads * 16 <= (1ull << 30)) grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
         if (reverse)
             quantize_quads_kernel<true><<<grid, kThreads, 0, st>>>((const float4*)x, (uint32_t*)q, nquads, scale, zp, scale_dev, zp_dev);
         else
@@ -348,20 +360,21 @@ __device__ __forceinline__ void store_f32x8(float* p, float4 a, float4 b) {
                  :: "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w), "l"(p) : "memory");
 }
 
+template <int UNROLL, bool STREAM_LOADS>
 __global__ void __launch_bounds__(kThreads)
 dequantize_octs_kernel(const uint2* __restrict__ q, float* __restrict__ out, uint64_t nocts, float scale, int32_t zp) {
-    const uint64_t step = (uint64_t)kThreads * kUnroll;
+    const uint64_t step = (uint64_t)kThreads * UNROLL;
     const uint64_t nsteps = (nocts + step - 1) / step;
     for (uint64_t s = blockIdx.x; s < nsteps; s += gridDim.x) {
         const uint64_t base = s * step + threadIdx.x;
-        uint2 w[kUnroll];
+        uint2 w[UNROLL];
         #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
+        for (int u = 0; u < UNROLL; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
-            if (i < nocts) w[u] = __ldcs(q + i);
+            if (i < nocts) w[u] = STREAM_LOADS ? __ldcs(q + i) : __ldg(q + i);
         }
         #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
+        for (int u = 0; u < UNROLL; u++) {
             uint64_t i = base + (uint64_t)u * kThreads;
             if (i < nocts) store_f32x8(out + i * 8, dequant_quad<true>(w[u].x, scale, zp), dequant_quad<true>(w[u].y, scale, zp));
         }
@@ -499,12 +512,14 @@ int rplb_dequantize_i8_f32(const int8_t* q, float* out, uint64_t n, float scale,
     if ((((uintptr_t)out & 31) == 0) && (((uintptr_t)q & 7) == 0) && n >= 8 &&
         zero_point > -(1 << 21) && zero_point < (1 << 21)) {
         const uint64_t nocts = n / 8;
-        unsigned int grid = stream_grid(nocts, (uint64_t)kThreads * kUnroll);
-        dequantize_octs_kernel<<<grid, kThreads, 0, st>>>((const uint2*)q, out, nocts, scale, zero_point);
+        // One CTA per step: for this write-heavy kernel a resident, striding grid was 13 % slower
+        // (5473 vs 6246 GB/s at 2^26 elements, 5759 vs 6771 at 2^30).
+        unsigned int grid = one_shot_grid(nocts, (uint64_t)kThreads * kUnroll);
+        dequantize_octs_kernel<kUnroll, true><<<grid, kThreads, 0, st>>>((const uint2*)q, out, nocts, scale, zero_point);
         if (int rc = launched("dequantize_octs_kernel")) return rc;
         nquads = nocts * 2;                 // the scalar kernel below takes what is left
     } else if (nquads) {
-        unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+        unsigned int grid = one_shot_grid(nquads, (uint64_t)kThreads * kUnroll);
         if (zero_point > -(1 << 21) && zero_point < (1 << 21))
             dequantize_quads_kernel<true><<<grid, kThreads, 0, st>>>((const uint32_t*)q, (float4*)out, nquads, scale, zero_point);
         else
@@ -528,7 +543,7 @@ int rplb_dequantize_per_channel_i8_f32(const int8_t* q, const float* scales, flo
     cudaStream_t st = as_stream(stream);
     const bool vec = (((uintptr_t)out & 15) == 0) && (((uintptr_t)q & 3) == 0) && (channel_size % 4 == 0);
     if (vec) {
-        unsigned int grid = stream_grid(n / 4, (uint64_t)kThreads * kUnroll);
+        unsigned int grid = one_shot_grid(n / 4, (uint64_t)kThreads * kUnroll);
         dequantize_pc_quads_kernel<<<grid, kThreads, 0, st>>>((const uint32_t*)q, scales, (float4*)out, n / 4, channel_size / 4);
         return launched("dequantize_pc_quads_kernel");
     }
