@@ -206,7 +206,9 @@ static int launch_minmax(const float* x, uint64_t n, rplb_qparams* params, cudaS
     head /= 4;
     if (head > n) head = n;
     uint64_t nquads = (n - head) / 4;
-    unsigned int grid = stream_grid(nquads, (uint64_t)kThreads * kUnroll);
+    // One CTA per 65536 elements (16 unrolled steps each) rather than a resident grid:
+    // measured 6172 vs 5974 GB/s at 2^26 elements, 7345 vs 7079 at 2^30.
+    unsigned int grid = one_shot_grid(nquads, (uint64_t)kThreads * kUnroll * 16);
     Scratch sc;
     if (int rc = scratch_for(st, (size_t)grid * sizeof(float2), &sc)) return rc;
     minmax_kernel<<<grid, kThreads, 0, st>>>(x, n, head, nquads, (float2*)sc.data, sc.control, params);
