@@ -247,3 +247,61 @@ class ShardedQuantizedLinear:
         if self.world == 1:
             return block
         return gather_columns(block, self.n_total, self.world, group)
+
+
+class HostPipeline:
+    """Back-to-back forward calls on host buffers with the PCIe directions overlapped.
+
+    ``forward_host`` finishes a call before the next one starts, so the host->device
+    copy of the next activation waits behind the device->host copy of the current
+    output although the link is full duplex.  Here every call is only enqueued
+    (``submit``): inputs and outputs are double-buffered on the device, the upload of
+    call n+1 runs on its own stream while call n computes and downloads, and
+    ``drain`` waits for everything.  Each call still uploads its whole activation and
+    downloads its whole output; results are the same bits as ``forward``.
+    """
+
+    def __init__(self, layer, rows, in_features, depth=2, row_chunks=8):
+        dev = layer.wq.device
+        self.layer, self.depth, self.row_chunks = layer, depth, row_chunks
+        self.din = [torch.empty((rows, in_features), dtype=torch.float32, device=dev) for _ in range(depth)]
+        self.dout = [torch.empty((rows, layer.wq.shape[0]), dtype=torch.float32, device=dev) for _ in range(depth)]
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.compute_done = [None] * depth
+        self.out_done = [None] * depth
+        self.calls = 0
+
+    def submit(self, x_host, out_host):
+        i = self.calls % self.depth
+        main = torch.cuda.current_stream(self.din[i].device)
+        if self.compute_done[i] is not None:
+            self.s_in.wait_event(self.compute_done[i])        # din[i] was last read by call n - depth
+        else:
+            self.s_in.wait_stream(main)
+        with torch.cuda.stream(self.s_in):
+            self.din[i].copy_(x_host, non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(self.s_in)
+        main.wait_event(uploaded)
+        if self.out_done[i] is not None:
+            main.wait_event(self.out_done[i])                 # dout[i] was last downloaded by call n - depth
+        dout = self.dout[i]
+
+        def ship(_, r0, r1):
+            ev = torch.cuda.Event()
+            ev.record(main)
+            self.s_out.wait_event(ev)
+            with torch.cuda.stream(self.s_out):
+                out_host[r0:r1].copy_(dout[r0:r1], non_blocking=True)
+
+        self.layer.forward(self.din[i], out=dout, row_chunks=self.row_chunks, after_chunk=ship)
+        self.compute_done[i] = torch.cuda.Event()
+        self.compute_done[i].record(main)
+        self.out_done[i] = torch.cuda.Event()
+        self.out_done[i].record(self.s_out)
+        self.calls += 1
+
+    def drain(self):
+        self.s_out.synchronize()
+        torch.cuda.current_stream(self.din[0].device).synchronize()
