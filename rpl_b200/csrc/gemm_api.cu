@@ -83,7 +83,12 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
     const bool want_tc = (backend >= 2 || big) && p.K && p.K % 16 == 0 && (((uintptr_t)p.A & 15) == 0) &&
                          (p.b_is_kn || (((uintptr_t)p.B & 15) == 0));
     const bool zero_points = p.mode == EPI_REQUANT_I32 && (p.za || p.zb);
-    if (want_tc && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535) {
+    // gemm_int8's B[K,N] goes to the tensor cores as it lies (MN-major operand) when its rows are
+    // 16-byte multiples and no zero points are involved; backends 4 and 5 (and zero points, whose
+    // column sums are taken from a K-contiguous copy) get the transposed copy instead.
+    const bool b_in_place = p.b_is_kn && !zero_points && p.N % 16 == 0 && (((uintptr_t)p.B & 15) == 0) &&
+                            (backend == 0 || backend == 2 || backend == 3);
+    if (want_tc && !b_in_place && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535) {
         // Library scratch: [ B as [N,K] | row sums of A | column sums of B ].
         const size_t bt_bytes = p.b_is_kn ? (((size_t)(p.K * p.N) + 255) & ~(size_t)255) : 0;
         const size_t rs_bytes = zero_points ? (((size_t)p.M * 4 + 255) & ~(size_t)255) : 0;

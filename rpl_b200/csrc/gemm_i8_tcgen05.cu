@@ -161,10 +161,20 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Descriptor of an MN-major operand tile (rows of the stage are K, the 128 bytes of
+// a row are 128 consecutive N) with the 128-byte swizzle: atoms of 8 K-rows x 128
+// bytes; leading byte offset = distance between 128-wide N blocks, stride byte
+// offset = distance between groups of 8 K-rows (1024 bytes).
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t n_block_stride_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((n_block_stride_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
 // Instruction descriptor: dense, no saturation, int32 accumulator (2 << 4),
 // A and B signed int8 (1 << 7, 1 << 10), both K-major, N >> 3 at bit 17,
 // M >> 4 at bit 24.
 constexpr uint32_t kIdescI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+constexpr uint32_t kIdescI8BMn = kIdescI8 | (1u << 16);      // B operand MN-major: gemm_int8's B[K,N] as it lies in memory
 
 // Tile index -> (m-tile, n-tile): tiles are numbered so that CTAs running at the
 // same time cover GROUP_M consecutive m-tiles of a few n-tiles, which keeps the
@@ -315,7 +325,13 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     uint8_t* b_dst = a_dst + A_STAGE_BYTES;
                     mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tm * TILE_M));
-                    tma_load_2d(b_dst, &map_w, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tn * TILE_N));
+                    if (!p.b_is_kn) {
+                        tma_load_2d(b_dst, &map_w, &sh->full[stage], (int32_t)(kb * TILE_K), (int32_t)(tn * TILE_N));
+                    } else {
+                        // B[K,N]: two boxes of 128 K-rows x 128 N-bytes, one per half of the 256 columns.
+                        tma_load_2d(b_dst, &map_w, &sh->full[stage], (int32_t)(tn * TILE_N), (int32_t)(kb * TILE_K));
+                        tma_load_2d(b_dst + B_STAGE_BYTES / 2, &map_w, &sh->full[stage], (int32_t)(tn * TILE_N + 128), (int32_t)(kb * TILE_K));
+                    }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -335,12 +351,22 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
                     const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
-                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + A_STAGE_BYTES);
-                    #pragma unroll
-                    for (int k = 0; k < TILE_K / MMA_K; k++) {
-                        // Inside a 128-byte swizzle row the next K slice starts 32 bytes on: +2 in units of 16 bytes.
-                        tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (MMA_K >> 4)), b_desc + (uint64_t)(k * (MMA_K >> 4)),
-                                  kIdescI8, (kb | (uint32_t)k) != 0 ? 1u : 0u);
+                    if (!p.b_is_kn) {
+                        const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + A_STAGE_BYTES);
+                        #pragma unroll
+                        for (int k = 0; k < TILE_K / MMA_K; k++) {
+                            // Inside a 128-byte swizzle row the next K slice starts 32 bytes on: +2 in units of 16 bytes.
+                            tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (MMA_K >> 4)), b_desc + (uint64_t)(k * (MMA_K >> 4)),
+                                      kIdescI8, (kb | (uint32_t)k) != 0 ? 1u : 0u);
+                        }
+                    } else {
+                        const uint64_t b_desc = make_mnmajor_sw128_desc(a_addr + A_STAGE_BYTES, B_STAGE_BYTES / 2);
+                        #pragma unroll
+                        for (int k = 0; k < TILE_K / MMA_K; k++) {
+                            // The next K slice of an MN-major tile is 32 rows of 128 bytes further on.
+                            tc_mma_i8(d_tmem, a_desc + (uint64_t)(k * (MMA_K >> 4)), b_desc + (uint64_t)(k * ((MMA_K * 128) >> 4)),
+                                      kIdescI8BMn, (kb | (uint32_t)k) != 0 ? 1u : 0u);
+                        }
                     }
                     tc_commit(&sh->empty[stage]);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -821,8 +847,24 @@ static int make_map(CUtensorMap* map, const int8_t* base, uint64_t rows, uint64_
     return 0;
 }
 
+// Map of gemm_int8's row-major B [K, N]: inner dimension N, box = 128 N-bytes x 128 K-rows.
+static int make_map_kn(CUtensorMap* map, const int8_t* base, uint64_t K, uint64_t N) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(RPLB_E_NO_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
+    cuuint64_t strides[1] = {(cuuint64_t)N};
+    cuuint32_t box[2] = {128, (cuuint32_t)TILE_K};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RPLB_E_BAD_ARG, "cuTensorMapEncodeTiled (B[K,N]) failed with CUresult %d", (int)r);
+    return 0;
+}
+
 bool gemm_tcgen05_supports(const GemmProblem& p) {
-    if (p.b_is_kn) return false;                                  // W must be [N,K]
+    // B as [K,N] is read in place by the 128 x 256 kernel (MN-major operand) when its rows are 16-byte multiples.
+    if (p.b_is_kn && (p.N % 16 != 0 || (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0)))) return false;
     if (p.M == 0 || p.N == 0 || p.K == 0) return false;
     if (p.K % 16 != 0) return false;                              // TMA: row stride in multiples of 16 bytes
     if (((uintptr_t)p.A & 15) || ((uintptr_t)p.B & 15)) return false;
@@ -976,6 +1018,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     const uint32_t num_kb = (uint32_t)((p.K + TILE_K - 1) / TILE_K);
     unsigned int sms = (unsigned int)sm_count();
     if (sms == 0) sms = 148;
+    if (p.b_is_kn) variant = 1;          // only the 128 x 256 kernel reads B[K,N] in place
     if (variant == 0) {
         // Measured on B200 (1000 W cap): un-throttled, the pair kernel keeps the
         // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster;
@@ -1011,7 +1054,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
     }
     if (int rc = make_map(&ma, p.A, p.M, p.K, TILE_M)) return rc;
-    if (int rc = make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
+    if (int rc = p.b_is_kn ? make_map_kn(&mw, p.B, p.K, p.N) : make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
     const uint32_t tiles_m = (uint32_t)((p.M + TILE_M - 1) / TILE_M);
     const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
     const uint64_t tiles = (uint64_t)tiles_m * tiles_n;

@@ -292,3 +292,22 @@ def test_bounded_wait_gives_up_and_reports(cuda, lib, port, backend):
     W = rng.integers(-128, 128, (256, 256), dtype=np.int8)
     D.gemm_backend(TC_SINGLE)
     assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W))
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (130, 304, 784), (37, 48, 144), (512, 512, 512), (1000, 1040, 2064),
+                                 (257, 16, 16)])
+def test_gemm_int8_reads_b_kn_in_place(cuda, lib, port, backend, mnk):
+    """gemm_int8's B [K,N] with N % 16 == 0 reaches the tensor cores without a transposed
+    copy (MN-major operand); ragged M, N and K tails included."""
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    for which in (TC_SINGLE, TC):
+        D.gemm_backend(which)
+        before = D.launch_count()
+        got = host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda), 0.013, 0.021, 0.37))
+        assert D.launch_count() - before == 1                  # the GEMM alone: no transpose pass
+        assert same(got, port.gemm_requant(A, B, 0.013, 0.021, 0.37)), which
+    assert same(host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda))), port.gemm_requant(A, B))
