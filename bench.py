@@ -518,6 +518,7 @@ def run_secondary(a):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     peaks = measured_peaks()
+    D.gemm_backend(a.gemm_backend)
     g = torch.Generator(device=dev)
     g.manual_seed(0x5EED0000 + int(a.workload[1]) * 16)
     one = lambda p: p[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]

@@ -146,3 +146,36 @@ def test_host_pipeline_equals_forward(cuda, lib):
     pipe.drain()
     for o, w in zip(ho, wants):
         assert torch.equal(o, w.cpu())
+
+
+def test_asymmetric_path_end_to_end(cuda, lib, port):
+    """tensor_quantize_int8_asymmetric on both operands, then gemm_int8 with their zero
+    points and scales (tensor-core path with the row/column-sum correction)."""
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(0x5EED0060)
+    M, K, N = 384, 512, 320
+    A = (rng.random((M, K), dtype=np.float32) * 4.0 - 1.0)          # skewed ranges: zero points far from 0
+    B = (rng.standard_normal((K, N)) * 0.3 + 0.5).astype(np.float32)
+    d = lambda a: torch.from_numpy(a).to(cuda)
+    qa, pa = D.quantize_asymmetric(d(A))
+    qb, pb = D.quantize_asymmetric(d(B))
+    ha, hb = pa.cpu().numpy(), pb.cpu().numpy()
+    sa, za = np.float32(ha[D.QPARAM_SCALE_ASYM]), int(ha.view(np.int32)[D.QPARAM_ZP_ASYM])
+    sb, zb = np.float32(hb[D.QPARAM_SCALE_ASYM]), int(hb.view(np.int32)[D.QPARAM_ZP_ASYM])
+    wqa, wsa, wza = port.quantize_asymmetric(A)
+    wqb, wsb, wzb = port.quantize_asymmetric(B)
+    assert (sa, za, sb, zb) == (wsa, wza, wsb, wzb) and za != 0 and zb != 0
+    assert same(host(qa), wqa) and same(host(qb), wqb)
+    sc = np.float32(sa * sb * 8)
+    prev = D.gemm_backend(0)
+    try:
+        for which in (1, 3, 4, 5):
+            D.gemm_backend(which)
+            got = host(D.gemm_i8_requant(qa, qb, sa, sb, sc, za, zb))
+            assert same(got, port.gemm_requant(wqa, wqb, sa, sb, sc, za, zb)), which
+    finally:
+        D.gemm_backend(prev)
+    # the requantized result tracks the fp32 product: |C*sc - A.B| is small next to |A.B|
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    err = np.abs(got.astype(np.float64) * float(sc) - ref)
+    assert err.mean() < 0.02 * np.abs(ref).mean()
