@@ -175,7 +175,7 @@ def test_asymmetric_path_end_to_end(cuda, lib, port):
             assert same(got, port.gemm_requant(wqa, wqb, sa, sb, sc, za, zb)), which
     finally:
         D.gemm_backend(prev)
-    # the requantized result tracks the fp32 product: |C*sc - A.B| is small next to |A.B|
-    ref = A.astype(np.float64) @ B.astype(np.float64)
-    err = np.abs(got.astype(np.float64) * float(sc) - ref)
-    assert err.mean() < 0.02 * np.abs(ref).mean()
+    # No accuracy claim is made here: the reference computes the zero point for a 0..255 range
+    # (src/rpl_quantization.c:102-104) but clamps to [-128,127] (src/rpl_core.c:524-525), so the upper
+    # part of a skewed tensor saturates.  Parity means reproducing that, which the checks above do.
+    assert int(host(qa).max()) == 127 and za > 0
