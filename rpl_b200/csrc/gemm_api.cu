@@ -55,6 +55,23 @@ __global__ void row_sums_i8_kernel(const int8_t* __restrict__ X, int32_t* __rest
     if (lane == 0) sums[row] = acc;
 }
 
+// sums[n] = sum_k B[k,n] of a row-major [K, N] int8 matrix: 32 consecutive columns per
+// CTA (coalesced along N), 8 K-slices per CTA folded through shared memory.
+__global__ void col_sums_i8_kernel(const int8_t* __restrict__ B, int32_t* __restrict__ sums, uint64_t K, uint64_t N) {
+    __shared__ int32_t part[8][33];
+    const uint64_t n = (uint64_t)blockIdx.x * 32 + threadIdx.x;
+    int32_t acc = 0;
+    if (n < N)
+        for (uint64_t k = threadIdx.y; k < K; k += 8) acc += (int32_t)__ldg(B + k * N + n);
+    part[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && n < N) {
+        #pragma unroll
+        for (int j = 1; j < 8; j++) acc += part[j][threadIdx.x];
+        sums[n] = acc;
+    }
+}
+
 // scale = absmax / 127.0f (src/rpl_quantization.c:87-88) from the value the GEMM epilogue accumulated.
 __global__ void absmax_to_scale_kernel(const float* __restrict__ absmax, float* __restrict__ scale) {
     *scale = __fdiv_rn(*absmax, 127.0f);
@@ -84,10 +101,22 @@ static int run_gemm(GemmProblem p, cudaStream_t st) {
                          (p.b_is_kn || (((uintptr_t)p.B & 15) == 0));
     const bool zero_points = p.mode == EPI_REQUANT_I32 && (p.za || p.zb);
     // gemm_int8's B[K,N] goes to the tensor cores as it lies (MN-major operand) when its rows are
-    // 16-byte multiples and no zero points are involved; backends 4 and 5 (and zero points, whose
-    // column sums are taken from a K-contiguous copy) get the transposed copy instead.
-    const bool b_in_place = p.b_is_kn && !zero_points && p.N % 16 == 0 && (((uintptr_t)p.B & 15) == 0) &&
+    // 16-byte multiples; backends 4 and 5 get a transposed, K-contiguous copy instead.
+    const bool b_in_place = p.b_is_kn && p.N % 16 == 0 && (((uintptr_t)p.B & 15) == 0) &&
                             (backend == 0 || backend == 2 || backend == 3);
+    if (want_tc && b_in_place && zero_points) {
+        // Row sums of A and column sums of B, both taken from the operands as they lie.
+        const size_t rs_bytes = ((size_t)p.M * 4 + 255) & ~(size_t)255;
+        Scratch sc;
+        if (int rc = scratch_for(st, rs_bytes + (size_t)p.N * 4, &sc)) return rc;
+        int32_t* rs = reinterpret_cast<int32_t*>(sc.data);
+        int32_t* cs = reinterpret_cast<int32_t*>(static_cast<char*>(sc.data) + rs_bytes);
+        if (int rc = launch_row_sums(p.A, rs, p.M, p.K, st)) return rc;
+        col_sums_i8_kernel<<<(unsigned int)((p.N + 31) / 32), dim3(32, 8), 0, st>>>(p.B, cs, p.K, p.N);
+        if (int rc = launched("col_sums_i8_kernel")) return rc;
+        q.a_row_sums = rs;
+        q.b_col_sums = cs;
+    }
     if (want_tc && !b_in_place && (p.b_is_kn || zero_points) && (p.K + 31) / 32 <= 65535) {
         // Library scratch: [ B as [N,K] | row sums of A | column sums of B ].
         const size_t bt_bytes = p.b_is_kn ? (((size_t)(p.K * p.N) + 255) & ~(size_t)255) : 0;

@@ -864,7 +864,7 @@ static int make_map_kn(CUtensorMap* map, const int8_t* base, uint64_t K, uint64_
 
 bool gemm_tcgen05_supports(const GemmProblem& p) {
     // B as [K,N] is read in place by the 128 x 256 kernel (MN-major operand) when its rows are 16-byte multiples.
-    if (p.b_is_kn && (p.N % 16 != 0 || (p.mode == EPI_REQUANT_I32 && (p.za != 0 || p.zb != 0)))) return false;
+    if (p.b_is_kn && p.N % 16 != 0) return false;
     if (p.M == 0 || p.N == 0 || p.K == 0) return false;
     if (p.K % 16 != 0) return false;                              // TMA: row stride in multiples of 16 bytes
     if (((uintptr_t)p.A & 15) || ((uintptr_t)p.B & 15)) return false;

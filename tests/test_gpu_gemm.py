@@ -201,7 +201,7 @@ def test_sampled_tiles_vs_checker_at_projection_size(cuda, lib, port, backend):
         assert same(host(Cd[m0:m0 + 128, n0:n0 + 128]), want)
 
 
-@pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (64, 40, 16)])
+@pytest.mark.parametrize("mnk", [(130, 300, 784), (512, 512, 512), (64, 40, 16), (130, 304, 784), (37, 48, 144)])
 @pytest.mark.parametrize("which", [TC_SINGLE, TC_PAIR, TC_WIDE])
 def test_zero_points_on_the_tensor_core_path(cuda, lib, port, backend, mnk, which):
     """gemm_int8 with za, zb != 0: the tensor-core kernels correct the plain product
