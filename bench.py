@@ -298,7 +298,7 @@ def run_ours(a):
     import torch.distributed as dist
 
     from rpl_b200 import device as D
-    from rpl_b200.sharded import HostPipeline, ShardedQuantizedLinear, shard_range
+    from rpl_b200.sharded import ShardedQuantizedLinear, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -439,29 +439,50 @@ def run_ours(a):
         else:
             xh.copy_(A)
             torch.cuda.synchronize()
-            # Calls are enqueued back to back through HostPipeline: every call uploads its whole
-            # activation and downloads its whole output; the upload of call n+1 overlaps the
-            # download of call n (PCIe is full duplex).
-            pipe = HostPipeline(layer, M, K)
-            pipe.submit(xh, oh)
-            pipe.drain()
+            # The reference-facing C ABI with host buffers: a QuantizedLinear layer over this rank's
+            # device-resident int8 weights, quantized_linear_submit_host / _drain.  Every call uploads
+            # its whole activation and downloads its whole output; the upload of call n+1 overlaps the
+            # download of call n (PCIe is full duplex).  Quantize and GEMM run on torch's current
+            # stream, which after the drain has also waited for the downloads, so the events see it all.
+            import ctypes as C
+            from rpl_b200 import capi
+            L = capi.load()
+            clayer = L.quantized_linear_wrap(wq.data_ptr(), wsc.data_ptr(), None, K, count)
+            if not clayer:
+                raise RuntimeError("quantized_linear_wrap failed")
+            estream = torch.cuda.Stream(device=dev)         # quantize and GEMM of the e2e calls run here
+            estream.wait_stream(torch.cuda.current_stream())
+            main = C.c_void_p(estream.cuda_stream)
+
+            def submit():
+                rc = L.quantized_linear_submit_host(clayer, xh.data_ptr(), M, oh.data_ptr(), False, main)
+                if rc != 0:
+                    raise RuntimeError("quantized_linear_submit_host failed with %d" % rc)
+
+            submit()
+            if L.quantized_linear_drain(clayer) != 0:
+                raise RuntimeError("quantized_linear_drain failed")
             esteps = max(2, min(a.steps, 6))
             barrier()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
+            launches_e0 = D.launch_count()
+            s0.record(estream)
             for _ in range(esteps):
-                pipe.submit(xh, oh)
-            pipe.drain()
-            s1.record()
+                submit()
+            if L.quantized_linear_drain(clayer) != 0:
+                raise RuntimeError("quantized_linear_drain failed")
+            s1.record(estream)
             barrier()
+            e2e_launches = D.launch_count() - launches_e0
             te = torch.tensor([s0.elapsed_time(s1) / esteps], device=dev)
             if world > 1:
                 dist.all_reduce(te, op=dist.ReduceOp.MAX)
             same = bool(torch.equal(oh[:256].to(dev), out[:256]))
             e2e = {"value": ops_total / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(te.item()),
                    "steps": esteps, "h2d_bytes_per_step": int(M * K * 4) * world, "d2h_bytes_per_step": int(M * N * 4),
-                   "api": "HostPipeline.submit / drain over ShardedQuantizedLinear (page-locked host buffers)", "matches_device_run": same}
-            del pipe
+                   "api": "quantized_linear_submit_host / quantized_linear_drain (C ABI, page-locked host buffers)",
+                   "matches_device_run": same, "gpu_launches": int(e2e_launches)}
+            L.quantized_linear_free(clayer)
         del xh, oh
 
     if rank != 0:

@@ -131,6 +131,12 @@ int  rplb_host_alloc(void** hptr, size_t bytes);     /* page-locked host memory 
 int  rplb_host_free(void* hptr);
 int  rplb_copy(void* dst, const void* src, size_t bytes, void* stream);   /* any direction, async */
 int  rplb_stream_sync(void* stream);
+int  rplb_stream_create(void** stream);              /* a non-blocking stream */
+int  rplb_stream_destroy(void* stream);
+int  rplb_event_create(void** event);                /* ordering only, no timing */
+int  rplb_event_destroy(void* event);
+int  rplb_event_record(void* event, void* stream);
+int  rplb_stream_wait_event(void* stream, void* event);
 /* 0 = ordinary host memory, 1 = page-locked host, 2 = device, 3 = managed */
 int  rplb_pointer_kind(const void* p);
 
@@ -369,6 +375,20 @@ typedef struct QuantizedLinear QuantizedLinear;
 QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bias);
 Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bool relu);
 void    quantized_linear_free(QuantizedLinear* layer);
+/* A layer over int8 weight rows [out,in], per-row scales and an optional fp32 bias
+ * that already live in device memory and remain the caller's. */
+QuantizedLinear* quantized_linear_wrap(const int8_t* weight_rows, const float* scales, const float* bias,
+                                       uint32_t in_features, uint32_t out_features);
+/* The same forward pass on host buffers, enqueued and pipelined: x [rows, in] and out
+ * [rows, out] in host memory (page-locked for full PCIe speed).  submit returns once
+ * the call is queued, drain waits for every queued call.  Inputs and outputs are
+ * double-buffered on the device, so the upload of call n+1 overlaps the compute and
+ * download of call n, and each row block of a call is downloaded while the next is in
+ * the GEMM.  compute_stream (a cudaStream_t, may be NULL) is where quantize and GEMM
+ * run; after drain it has also waited for the downloads.  Both return 0 or an error code. */
+int     quantized_linear_submit_host(QuantizedLinear* layer, const float* x, uint32_t rows, float* out, bool relu,
+                                     void* compute_stream);
+int     quantized_linear_drain(QuantizedLinear* layer);
 
 /* Quantized weights on disk, in the framing of the reference's fp32 checkpoint
  * writer (checkpoint_save_model, src/rpl_training.c:915-944; the reference has

@@ -88,6 +88,12 @@ SIGNATURES = {
     "rplb_host_free": ("rc", [_vp]),
     "rplb_copy": ("rc", [_vp, _vp, _sz, _vp]),
     "rplb_stream_sync": ("rc", [_vp]),
+    "rplb_stream_create": ("rc", [C.POINTER(_vp)]),
+    "rplb_stream_destroy": ("rc", [_vp]),
+    "rplb_event_create": ("rc", [C.POINTER(_vp)]),
+    "rplb_event_destroy": ("rc", [_vp]),
+    "rplb_event_record": ("rc", [_vp, _vp]),
+    "rplb_stream_wait_event": ("rc", [_vp, _vp]),
     "rplb_pointer_kind": (C.c_int, [_vp]),
     "rplb_minmax_f32": ("rc", [_vp, _u64, _vp, _vp]),
     "rplb_minmax_f32_static": ("rc", [_vp, _u64, _vp, _vp]),
@@ -140,6 +146,9 @@ SIGNATURES = {
     "quantized_linear_create": (_vp, [_TP, _TP]),
     "quantized_linear_forward": (_TP, [_vp, _TP, C.c_bool]),
     "quantized_linear_free": (None, [_vp]),
+    "quantized_linear_wrap": (_vp, [_vp, _vp, _vp, C.c_uint32, C.c_uint32]),
+    "quantized_linear_submit_host": (C.c_int, [_vp, _vp, C.c_uint32, _vp, C.c_bool, _vp]),
+    "quantized_linear_drain": (C.c_int, [_vp]),
     "quantized_weights_save": (C.c_int, [C.c_char_p, C.POINTER(_PP), C.c_uint32]),
     "quantized_weights_load": (C.POINTER(_PP), [C.c_char_p, C.POINTER(C.c_uint32), C.c_bool]),
 }

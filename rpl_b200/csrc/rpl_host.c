@@ -644,20 +644,62 @@ PerChannelQuantizedTensor** quantized_weights_load(const char* path, uint32_t* n
  * activation per tensor (tensor_quantize_int8_symmetric's arithmetic) and runs
  * the INT8 GEMM with the fused dequantize + bias (+ ReLU) epilogue.
  * ---------------------------------------------------------------------- */
+#define QL_DEPTH 2          /* calls in flight in the host-buffer pipeline */
+#define QL_BLOCKS 8         /* row blocks per call: a block is downloaded while the next one computes */
+
 struct QuantizedLinear {
     PerChannelQuantizedTensor* weight;   /* device-resident int8 rows, scales, zero points */
     float*   bias;                       /* device, out_features floats, or NULL */
     uint32_t in_features;
     uint32_t out_features;
+    int      owns_weight;                /* 0 when the int8 rows / scales / bias belong to the caller */
     int8_t*  act;                        /* device buffer for the quantized activation */
     size_t   act_capacity;
     rplb_qparams* act_params;            /* device */
+    /* host-buffer pipeline (quantized_linear_submit_host / _drain) */
+    void*    s_main;                     /* compute stream: the caller's, or one owned by the layer */
+    int      owns_main;
+    void*    s_in;                       /* uploads */
+    void*    s_out;                      /* downloads */
+    float*   din[QL_DEPTH];              /* device copies of the activations in flight */
+    float*   dout[QL_DEPTH];             /* device outputs in flight */
+    size_t   din_capacity[QL_DEPTH], dout_capacity[QL_DEPTH];
+    void*    ev_uploaded[QL_DEPTH];
+    void*    ev_computed[QL_DEPTH];
+    void*    ev_downloaded[QL_DEPTH];
+    void*    ev_block[QL_DEPTH][QL_BLOCKS];
+    int      slot_used[QL_DEPTH];
+    uint64_t calls;
 };
+
+static void quantized_linear_release_pipeline(QuantizedLinear* layer) {
+    if (layer->s_in) {                   /* nothing may be in flight when buffers and streams go */
+        rplb_stream_sync(layer->s_in);
+        rplb_stream_sync(layer->s_main);
+        rplb_stream_sync(layer->s_out);
+    }
+    for (int i = 0; i < QL_DEPTH; i++) {
+        rplb_free(layer->din[i]);
+        rplb_free(layer->dout[i]);
+        rplb_event_destroy(layer->ev_uploaded[i]);
+        rplb_event_destroy(layer->ev_computed[i]);
+        rplb_event_destroy(layer->ev_downloaded[i]);
+        for (int b = 0; b < QL_BLOCKS; b++) rplb_event_destroy(layer->ev_block[i][b]);
+    }
+    rplb_stream_destroy(layer->s_in);
+    rplb_stream_destroy(layer->s_out);
+    if (layer->owns_main) rplb_stream_destroy(layer->s_main);
+}
 
 void quantized_linear_free(QuantizedLinear* layer) {
     if (!layer) return;
-    per_channel_quantized_tensor_free(layer->weight);
-    rplb_free(layer->bias);
+    quantized_linear_release_pipeline(layer);
+    if (layer->owns_weight) {
+        per_channel_quantized_tensor_free(layer->weight);
+        rplb_free(layer->bias);
+    } else {
+        free(layer->weight);             /* the struct only; its blocks are the caller's */
+    }
     rplb_free(layer->act);
     rplb_free(layer->act_params);
     free(layer);
@@ -671,6 +713,7 @@ QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bia
     if (!layer) return NULL;
     layer->out_features = weight->shape[0];
     layer->in_features = weight->shape[1];
+    layer->owns_weight = 1;
     /* Quantize on the device and keep the result there: a device-resident input
      * makes tensor_quantize_per_channel return device-resident blocks. */
     Tensor* wdev = on_device(weight->data) ? NULL : tensor_upload(weight);
@@ -696,6 +739,7 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
     if (!layer || !input || input->dims < 1 || input->size % layer->in_features != 0) return NULL;
     t_last_error = 0;
     const char* who = "quantized_linear_forward";
+    if (quantized_linear_drain(layer) != 0) return NULL;      /* nothing of the host pipeline may be in flight */
     const size_t K = layer->in_features, N = layer->out_features, M = input->size / K;
     const int dev_in = on_device(input->data);
     uint32_t out_shape[2] = {(uint32_t)M, (uint32_t)N};                      /* src/rpl_nn.c:57 */
@@ -722,4 +766,137 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
         return NULL;
     }
     return out;
+}
+
+/* A layer over int8 weight rows, scales and bias that already live in device
+ * memory and stay the caller's (nothing is copied, nothing is freed by
+ * quantized_linear_free). */
+QuantizedLinear* quantized_linear_wrap(const int8_t* weight_rows, const float* scales, const float* bias,
+                                       uint32_t in_features, uint32_t out_features) {
+    if (!weight_rows || !scales || !on_device(weight_rows) || !on_device(scales) || (bias && !on_device(bias))) return NULL;
+    t_last_error = 0;
+    QuantizedLinear* layer = (QuantizedLinear*)calloc(1, sizeof(QuantizedLinear));
+    PerChannelQuantizedTensor* w = (PerChannelQuantizedTensor*)calloc(1, sizeof(PerChannelQuantizedTensor));
+    void* params = NULL;
+    if (!layer || !w || report(rplb_malloc(&params, sizeof(rplb_qparams)), "quantized_linear_wrap") != 0) {
+        free(layer);
+        free(w);
+        return NULL;
+    }
+    w->data = (int8_t*)weight_rows;
+    w->scales = (float*)scales;
+    w->num_channels = out_features;
+    w->channel_size = in_features;
+    w->dims = 2;
+    w->shape[0] = out_features;
+    w->shape[1] = in_features;
+    layer->weight = w;
+    layer->bias = (float*)bias;
+    layer->in_features = in_features;
+    layer->out_features = out_features;
+    layer->act_params = (rplb_qparams*)params;
+    return layer;
+}
+
+/* Streams and events of the host-buffer pipeline, created on first use.
+ * compute_stream: the stream quantize and GEMM run on (a cudaStream_t); NULL lets the layer own one. */
+static int quantized_linear_pipeline_ready(QuantizedLinear* layer, void* compute_stream, const char* who) {
+    if (layer->s_in) {
+        if (compute_stream && compute_stream != layer->s_main) {
+            if (report(rplb_stream_sync(layer->s_main), who)) return -1;
+            if (layer->owns_main) rplb_stream_destroy(layer->s_main);
+            layer->s_main = compute_stream;
+            layer->owns_main = 0;
+        }
+        return 0;
+    }
+    if (compute_stream) { layer->s_main = compute_stream; layer->owns_main = 0; }
+    else { if (report(rplb_stream_create(&layer->s_main), who)) return -1; layer->owns_main = 1; }
+    if (report(rplb_stream_create(&layer->s_out), who) || report(rplb_stream_create(&layer->s_in), who)) return -1;
+    for (int i = 0; i < QL_DEPTH; i++) {
+        if (report(rplb_event_create(&layer->ev_uploaded[i]), who) || report(rplb_event_create(&layer->ev_computed[i]), who) ||
+            report(rplb_event_create(&layer->ev_downloaded[i]), who)) return -1;
+        for (int b = 0; b < QL_BLOCKS; b++)
+            if (report(rplb_event_create(&layer->ev_block[i][b]), who)) return -1;
+    }
+    return 0;
+}
+
+static int grow_device(void** p, size_t* cap, size_t bytes, const char* who) {
+    if (*cap >= bytes) return 0;
+    rplb_free(*p);
+    *p = NULL;
+    *cap = 0;
+    if (report(rplb_malloc(p, bytes), who)) return -1;
+    *cap = bytes;
+    return 0;
+}
+
+/* y = x . W^T + b on host buffers, enqueued: x is [rows, in_features] fp32 and out
+ * [rows, out_features] fp32, both in host memory (page-locked for full PCIe speed).
+ * The call returns once everything is queued; quantized_linear_drain waits.  Inputs
+ * and outputs are double-buffered on the device: the upload of call n+1 overlaps the
+ * compute and download of call n, and within a call each row block is downloaded
+ * while the next one is in the GEMM.  x must stay valid until its upload has run and
+ * out must not be read before the drain.  Returns 0, or the error code also kept by
+ * rpl_cuda_last_error(). */
+int quantized_linear_submit_host(QuantizedLinear* layer, const float* x, uint32_t rows, float* out, bool relu,
+                                 void* compute_stream) {
+    if (!layer || !x || !out) return RPLB_E_BAD_ARG;
+    if (rows == 0) return 0;
+    t_last_error = 0;
+    const char* who = "quantized_linear_submit_host";
+    if (quantized_linear_pipeline_ready(layer, compute_stream, who)) return t_last_error;
+    const size_t K = layer->in_features, N = layer->out_features, M = rows;
+    const int i = (int)(layer->calls % QL_DEPTH);
+    if (layer->din_capacity[i] < M * K * 4 || layer->dout_capacity[i] < M * N * 4 || layer->act_capacity < M * K) {
+        /* Buffers change size only with everything idle. */
+        if (report(rplb_stream_sync(layer->s_in), who) || report(rplb_stream_sync(layer->s_main), who) ||
+            report(rplb_stream_sync(layer->s_out), who)) return t_last_error;
+        if (grow_device((void**)&layer->din[i], &layer->din_capacity[i], M * K * 4, who) ||
+            grow_device((void**)&layer->dout[i], &layer->dout_capacity[i], M * N * 4, who) ||
+            grow_device((void**)&layer->act, &layer->act_capacity, M * K, who)) return t_last_error;
+    }
+    float* din = layer->din[i];
+    float* dout = layer->dout[i];
+    if (layer->slot_used[i] && report(rplb_stream_wait_event(layer->s_in, layer->ev_computed[i]), who)) return t_last_error;
+    if (report(rplb_copy(din, x, M * K * 4, layer->s_in), who) || report(rplb_event_record(layer->ev_uploaded[i], layer->s_in), who) ||
+        report(rplb_stream_wait_event(layer->s_main, layer->ev_uploaded[i]), who)) return t_last_error;
+    if (layer->slot_used[i] && report(rplb_stream_wait_event(layer->s_main, layer->ev_downloaded[i]), who)) return t_last_error;
+    if (report(rplb_quantize_symmetric_f32_i8(din, layer->act, M * K, layer->act_params, layer->s_main), who)) return t_last_error;
+    size_t step = (M + QL_BLOCKS - 1) / QL_BLOCKS;
+    step = (step + 127) / 128 * 128;
+    int b = 0;
+    for (size_t r0 = 0; r0 < M; r0 += step, b++) {
+        const size_t r1 = r0 + step < M ? r0 + step : M;
+        if (report(rplb_linear_i8_dequant_f32(layer->act + r0 * K, layer->weight->data, dout + r0 * N, r1 - r0, K, N, N,
+                                              &layer->act_params->scale_sym, layer->weight->scales, layer->bias,
+                                              relu ? 1 : 0, layer->s_main), who) ||
+            report(rplb_event_record(layer->ev_block[i][b], layer->s_main), who) ||
+            report(rplb_stream_wait_event(layer->s_out, layer->ev_block[i][b]), who) ||
+            report(rplb_copy(out + r0 * N, dout + r0 * N, (r1 - r0) * N * 4, layer->s_out), who)) return t_last_error;
+    }
+    if (report(rplb_event_record(layer->ev_computed[i], layer->s_main), who) ||
+        report(rplb_event_record(layer->ev_downloaded[i], layer->s_out), who)) return t_last_error;
+    layer->slot_used[i] = 1;
+    layer->calls++;
+    return 0;
+}
+
+/* Waits until every submitted call has delivered its output.  The compute stream is
+ * made to wait for the downloads first, so an event recorded on it after this call
+ * also covers them. */
+int quantized_linear_drain(QuantizedLinear* layer) {
+    if (!layer || !layer->s_in) return 0;
+    const char* who = "quantized_linear_drain";
+    for (int i = 0; i < QL_DEPTH; i++)
+        if (layer->slot_used[i] && report(rplb_stream_wait_event(layer->s_main, layer->ev_downloaded[i]), who)) return t_last_error;
+    if (report(rplb_stream_sync(layer->s_out), who) || report(rplb_stream_sync(layer->s_main), who)) return t_last_error;
+    int st = rplb_kernel_status(1);
+    if (st != 0) {
+        t_last_error = RPLB_E_KERNEL;
+        fprintf(stderr, "rpl (cuda): %s: a kernel gave up waiting (code %d)\n", who, st);
+        return RPLB_E_KERNEL;
+    }
+    return 0;
 }

@@ -128,6 +128,34 @@ int rplb_copy(void* dst, const void* src, size_t bytes, void* stream) {
 
 int rplb_stream_sync(void* stream) { return cuda_ok(cudaStreamSynchronize(as_stream(stream)), "cudaStreamSynchronize"); }
 
+int rplb_stream_create(void** stream) {
+    if (!stream) return fail(RPLB_E_BAD_ARG, "rplb_stream_create: null result pointer");
+    cudaStream_t s = nullptr;
+    if (int rc = cuda_ok(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreateWithFlags")) return rc;
+    *stream = s;
+    return 0;
+}
+
+int rplb_stream_destroy(void* stream) { return stream ? cuda_ok(cudaStreamDestroy(as_stream(stream)), "cudaStreamDestroy") : 0; }
+
+int rplb_event_create(void** event) {
+    if (!event) return fail(RPLB_E_BAD_ARG, "rplb_event_create: null result pointer");
+    cudaEvent_t e = nullptr;
+    if (int rc = cuda_ok(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreateWithFlags")) return rc;
+    *event = e;
+    return 0;
+}
+
+int rplb_event_destroy(void* event) { return event ? cuda_ok(cudaEventDestroy(static_cast<cudaEvent_t>(event)), "cudaEventDestroy") : 0; }
+
+int rplb_event_record(void* event, void* stream) {
+    return cuda_ok(cudaEventRecord(static_cast<cudaEvent_t>(event), as_stream(stream)), "cudaEventRecord");
+}
+
+int rplb_stream_wait_event(void* stream, void* event) {
+    return cuda_ok(cudaStreamWaitEvent(as_stream(stream), static_cast<cudaEvent_t>(event), 0), "cudaStreamWaitEvent");
+}
+
 int rplb_pointer_kind(const void* p) {
     if (!p) return 0;
     cudaPointerAttributes a;

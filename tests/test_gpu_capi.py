@@ -233,3 +233,37 @@ def test_quantized_linear_layers_chain_like_the_mlp(cuda, lib, port):
         lib.tensor_free(t)
     lib.quantized_linear_free(l1)
     lib.quantized_linear_free(l2)
+
+
+def test_quantized_linear_host_pipeline(cuda, lib, port):
+    """quantized_linear_submit_host / _drain: several calls in flight on page-locked
+    host buffers, double-buffered on the device, each equal to the checker's result."""
+    rng = np.random.default_rng(41)
+    M, K, N = 1000, 256, 384
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    tw, tb = host_tensor(lib, W), host_tensor(lib, bias)
+    layer = lib.quantized_linear_create(tw, tb)
+    wq, ws, _ = port.quantize_per_channel(W, N)
+    xs = [torch.from_numpy((rng.standard_normal((M, K)) * (i + 1)).astype(np.float32)).pin_memory() for i in range(5)]
+    outs = [torch.empty((M, N), dtype=torch.float32).pin_memory() for _ in xs]
+    for x, o in zip(xs, outs):
+        assert lib.quantized_linear_submit_host(layer, x.data_ptr(), M, o.data_ptr(), True, None) == 0
+    assert lib.quantized_linear_drain(layer) == 0
+    for x, o in zip(xs, outs):
+        xq, s = port.quantize_symmetric(x.numpy())
+        assert same(o.numpy(), port.linear_dequant(xq, wq, s, ws, bias, relu=True))
+    # a different row count afterwards (buffers grow), then the blocking call on the same layer
+    x2 = torch.from_numpy(rng.standard_normal((2 * M + 7, K)).astype(np.float32)).pin_memory()
+    o2 = torch.empty((2 * M + 7, N), dtype=torch.float32).pin_memory()
+    assert lib.quantized_linear_submit_host(layer, x2.data_ptr(), 2 * M + 7, o2.data_ptr(), False, None) == 0
+    assert lib.quantized_linear_drain(layer) == 0
+    xq, s = port.quantize_symmetric(x2.numpy())
+    assert same(o2.numpy(), port.linear_dequant(xq, wq, s, ws, bias, relu=False))
+    t = host_tensor(lib, xs[0].numpy())
+    y = lib.quantized_linear_forward(layer, t, True)
+    assert same(read_host(y.contents.data, (M, N), np.float32), outs[0].numpy())
+    for p in (t, y, tw, tb):
+        lib.tensor_free(p)
+    lib.quantized_linear_free(layer)
+    assert lib.rpl_cuda_last_error() == 0
