@@ -302,6 +302,20 @@ void    tensor_free(Tensor* t);
 void*   rpitorch_aligned_alloc(size_t alignment, size_t size);
 void    rpitorch_aligned_free(void* ptr);
 
+/* include/rpl.h:105-108, src/rpl_gpu.c:88-229 (the reference's accelerator
+ * hooks).  rpl_gpu_init reports whether a CUDA device is present.
+ * tensor_to_gpu gives the tensor a mirror in device memory, named by
+ * Tensor.gpu_buffer, and sets Tensor.device = DEVICE_GPU; the host block
+ * stays.  Every entry point below that takes a Tensor then works on the
+ * mirror and returns device-resident results.  tensor_from_gpu copies the
+ * mirror back into the host block (the tensor stays mirrored, as in the
+ * reference); tensor_free releases the mirror.  rpl_gpu_shutdown frees the
+ * calling thread's staging buffers. */
+bool    rpl_gpu_init(void);
+void    rpl_gpu_shutdown(void);
+void    tensor_to_gpu(Tensor* t);
+void    tensor_from_gpu(Tensor* t);
+
 /* include/rpl.h:176, src/rpl_core.c:511-530 */
 QuantizedTensor* tensor_quantize_int8(const Tensor* input, float scale, int32_t zero_point);
 /* include/rpl.h:177, src/ops_extended.c:75-80 */

@@ -119,6 +119,10 @@ SIGNATURES = {
     "tensor_free": (None, [_TP]),
     "rpitorch_aligned_alloc": (_vp, [_sz, _sz]),
     "rpitorch_aligned_free": (None, [_vp]),
+    "rpl_gpu_init": (C.c_bool, []),
+    "rpl_gpu_shutdown": (None, []),
+    "tensor_to_gpu": (None, [_TP]),
+    "tensor_from_gpu": (None, [_TP]),
     "tensor_quantize_int8": (_QP, [_TP, _f, _i]),
     "quantized_tensor_free": (None, [_QP]),
     "tensor_get_min_max": (None, [_TP, f32p, f32p]),

@@ -19,6 +19,7 @@
 #include "rpl_b200.h"
 #include <float.h>
 #include <math.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -99,6 +100,96 @@ static const void* to_device(int slot, const void* p, size_t bytes) {
 }
 
 /* ------------------------------------------------------------------------
+ * Device mirrors: include/rpl.h:105-108, src/rpl_gpu.c:88-229.
+ *
+ * The reference's accelerator keeps a Tensor's host block and adds a buffer
+ * object named by the 32-bit Tensor.gpu_buffer.  Here that field indexes a
+ * table of device blocks; every entry point that takes a Tensor works on the
+ * mirror when there is one, and then leaves its results in device memory.
+ * ---------------------------------------------------------------------- */
+#define MIRROR_MAX 65536u
+static pthread_mutex_t g_mirror_mu = PTHREAD_MUTEX_INITIALIZER;
+static void*    g_mirror[MIRROR_MAX];          /* handle h lives in g_mirror[h - 1] */
+static uint32_t g_mirror_hint = 0;
+
+static void* mirror_of(const Tensor* t) {
+    if (t->device != DEVICE_GPU || t->gpu_buffer == 0 || t->gpu_buffer > MIRROR_MAX) return NULL;
+    pthread_mutex_lock(&g_mirror_mu);
+    void* d = g_mirror[t->gpu_buffer - 1];
+    pthread_mutex_unlock(&g_mirror_mu);
+    return d;
+}
+
+/* Where the tensor's elements are to be read or written by the device. */
+static float* tensor_data(const Tensor* t) {
+    void* d = mirror_of(t);
+    return d ? (float*)d : t->data;
+}
+
+static void mirror_release(Tensor* t) {
+    if (t->device != DEVICE_GPU || t->gpu_buffer == 0 || t->gpu_buffer > MIRROR_MAX) return;
+    pthread_mutex_lock(&g_mirror_mu);
+    void* d = g_mirror[t->gpu_buffer - 1];
+    g_mirror[t->gpu_buffer - 1] = NULL;
+    pthread_mutex_unlock(&g_mirror_mu);
+    if (d) rplb_free(d);
+    t->gpu_buffer = 0;
+    t->device = DEVICE_CPU;
+}
+
+bool rpl_gpu_init(void) { return rplb_device_count() > 0; }
+
+/* Releases the calling thread's staging buffers.  Mirrors belong to their
+ * tensors and go with tensor_free. */
+void rpl_gpu_shutdown(void) {
+    rplb_stream_sync(NULL);
+    for (int i = 0; i < STAGE_SLOTS; i++) {
+        if (t_stage[i]) rplb_free(t_stage[i]);
+        t_stage[i] = NULL;
+        t_stage_cap[i] = 0;
+    }
+}
+
+void tensor_to_gpu(Tensor* t) {
+    if (!t) return;
+    if (t->device == DEVICE_GPU) return;                 /* mirrored already, or born in device memory */
+    t_last_error = 0;
+    const size_t bytes = (size_t)t->size * sizeof(float);
+    void* d = NULL;
+    if (report(rplb_malloc(&d, bytes), "tensor_to_gpu") != 0) return;
+    if (report(rplb_copy(d, t->data, bytes, NULL), "tensor_to_gpu") != 0 || finish("tensor_to_gpu") != 0) {
+        rplb_free(d);
+        return;
+    }
+    uint32_t h = 0;
+    pthread_mutex_lock(&g_mirror_mu);
+    for (uint32_t i = 0; i < MIRROR_MAX; i++) {
+        uint32_t slot = (g_mirror_hint + i) % MIRROR_MAX;
+        if (!g_mirror[slot]) { g_mirror[slot] = d; h = slot + 1; g_mirror_hint = slot + 1; break; }
+    }
+    pthread_mutex_unlock(&g_mirror_mu);
+    if (h == 0) {
+        rplb_free(d);
+        t_last_error = RPLB_E_TOO_LARGE;
+        fprintf(stderr, "rpl (cuda): tensor_to_gpu failed: %u tensors are mirrored already\n", MIRROR_MAX);
+        return;
+    }
+    t->gpu_buffer = h;
+    t->device = DEVICE_GPU;
+}
+
+/* Copies the mirror back into the host block; the tensor stays mirrored, as
+ * in the reference (src/rpl_gpu.c:217-229). */
+void tensor_from_gpu(Tensor* t) {
+    if (!t || t->device == DEVICE_CPU) return;
+    void* d = mirror_of(t);
+    if (!d) return;                                      /* born in device memory: no host block to fill */
+    t_last_error = 0;
+    if (report(rplb_copy(t->data, d, (size_t)t->size * sizeof(float), NULL), "tensor_from_gpu") != 0) return;
+    finish("tensor_from_gpu");
+}
+
+/* ------------------------------------------------------------------------
  * Allocation glue: src/rpl_core.c:33-77.
  * ---------------------------------------------------------------------- */
 void* rpitorch_aligned_alloc(size_t alignment, size_t size) {
@@ -159,6 +250,7 @@ Tensor* tensor_create_device(uint32_t dims, const uint32_t* shape) {
 
 void tensor_free(Tensor* t) {
     if (!t) return;
+    mirror_release(t);
     if (t->_allocation) rpitorch_aligned_free(t->_allocation);
     if (t->grad) rpitorch_aligned_free(t->grad);
     free(t);
@@ -177,7 +269,7 @@ Tensor* tensor_download(const Tensor* dev) {
     if (!dev) return NULL;
     Tensor* h = tensor_create(dev->dims, dev->shape, false);
     if (!h) return NULL;
-    if (report(rplb_copy(h->data, dev->data, (size_t)dev->size * 4, NULL), "tensor_download") != 0 ||
+    if (report(rplb_copy(h->data, tensor_data(dev), (size_t)dev->size * 4, NULL), "tensor_download") != 0 ||
         finish("tensor_download") != 0) { tensor_free(h); return NULL; }
     return h;
 }
@@ -201,11 +293,12 @@ static QuantizedTensor* quantize_common(const Tensor* input, int how, float scal
     if (!input) return NULL;
     t_last_error = 0;
     const size_t n = input->size;
-    const int dev_in = on_device(input->data);
+    const float* src = tensor_data(input);
+    const int dev_in = on_device(src);
     QuantizedTensor* qt = new_qt_like(input);
     if (!qt) return NULL;
 
-    const float* x = (const float*)to_device(0, input->data, n * 4);
+    const float* x = (const float*)to_device(0, src, n * 4);
     int8_t* q_dev = NULL;
     void* own_q = NULL;
     if (dev_in) {
@@ -260,7 +353,7 @@ void quantized_tensor_free(QuantizedTensor* qt) {
 /* min/max of the device reduction, fetched to the host. */
 static int minmax_to_host(const Tensor* t, rplb_qparams* hp, const char* who) {
     const size_t n = t->size;
-    const float* x = (const float*)to_device(0, t->data, n * 4);
+    const float* x = (const float*)to_device(0, tensor_data(t), n * 4);
     rplb_qparams* params = (rplb_qparams*)stage(2, sizeof(rplb_qparams));
     if ((n && !x) || !params) return -1;
     if (report(rplb_minmax_f32(x, n, params, NULL), who) != 0) return -1;
@@ -314,10 +407,11 @@ PerChannelQuantizedTensor* tensor_quantize_per_channel(const Tensor* input, uint
     qt->dims = input->dims;
     memcpy(qt->shape, input->shape, input->dims * sizeof(uint32_t));
     const size_t n = input->size, C = qt->num_channels;
-    const int dev_in = on_device(input->data);
+    const float* src = tensor_data(input);
+    const int dev_in = on_device(src);
     const char* who = "tensor_quantize_per_channel";
 
-    const float* x = (const float*)to_device(0, input->data, n * 4);
+    const float* x = (const float*)to_device(0, src, n * 4);
     void *q_dev = NULL, *s_dev = NULL, *z_dev = NULL;
     if (dev_in) {
         if (report(rplb_malloc(&q_dev, n), who) || report(rplb_malloc(&s_dev, C * 4), who) || report(rplb_malloc(&z_dev, C * 4), who)) goto fail;
@@ -452,8 +546,9 @@ void tensor_relu_inplace(Tensor* t) {
     t_last_error = 0;
     const char* who = "tensor_relu_inplace";
     const size_t n = t->size;
-    if (on_device(t->data)) {
-        if (report(rplb_relu_f32_inplace(t->data, n, NULL), who) == 0) finish(who);
+    float* resident = tensor_data(t);
+    if (on_device(resident)) {
+        if (report(rplb_relu_f32_inplace(resident, n, NULL), who) == 0) finish(who);
         return;
     }
     float* d = (float*)stage(0, n * 4);
@@ -716,7 +811,7 @@ QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bia
     layer->owns_weight = 1;
     /* Quantize on the device and keep the result there: a device-resident input
      * makes tensor_quantize_per_channel return device-resident blocks. */
-    Tensor* wdev = on_device(weight->data) ? NULL : tensor_upload(weight);
+    Tensor* wdev = on_device(tensor_data(weight)) ? NULL : tensor_upload(weight);
     layer->weight = tensor_quantize_per_channel(wdev ? wdev : weight, 0);
     tensor_free(wdev);
     void* params = NULL;
@@ -725,7 +820,7 @@ QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bia
     if (bias) {
         void* b = NULL;
         if (bias->size != layer->out_features || report(rplb_malloc(&b, (size_t)bias->size * 4), who) != 0 ||
-            report(rplb_copy(b, bias->data, (size_t)bias->size * 4, NULL), who) != 0 || finish(who) != 0) {
+            report(rplb_copy(b, tensor_data(bias), (size_t)bias->size * 4, NULL), who) != 0 || finish(who) != 0) {
             rplb_free(b);
             quantized_linear_free(layer);
             return NULL;
@@ -741,7 +836,8 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
     const char* who = "quantized_linear_forward";
     if (quantized_linear_drain(layer) != 0) return NULL;      /* nothing of the host pipeline may be in flight */
     const size_t K = layer->in_features, N = layer->out_features, M = input->size / K;
-    const int dev_in = on_device(input->data);
+    const float* src = tensor_data(input);
+    const int dev_in = on_device(src);
     uint32_t out_shape[2] = {(uint32_t)M, (uint32_t)N};                      /* src/rpl_nn.c:57 */
     Tensor* out = dev_in ? tensor_create_device(2, out_shape) : tensor_create(2, out_shape, false);
     if (!out) return NULL;
@@ -755,7 +851,7 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
         layer->act = (int8_t*)a;
         layer->act_capacity = M * K;
     }
-    const float* x = (const float*)to_device(0, input->data, M * K * 4);
+    const float* x = (const float*)to_device(0, src, M * K * 4);
     float* o = dev_in ? out->data : (float*)stage(3, M * N * 4);
     if ((M * K && !x) || !o) { tensor_free(out); return NULL; }
     if (report(rplb_quantize_symmetric_f32_i8(x, layer->act, M * K, layer->act_params, NULL), who) != 0 ||

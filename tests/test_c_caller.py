@@ -69,7 +69,7 @@ def test_combined_library_keeps_the_rest_of_the_reference(tmp_path, lib):
             continue
         o = str(tmp_path / (name + ".o"))
         subprocess.run(["/usr/bin/gcc", "-O1", "-fopenmp", "-fPIC", "-w", "-I", REF_INCLUDE, "-c", src, "-o", o], check=True)
-        if name in ("rpl_core", "ops_extended", "rpl_quantization"):
+        if name in ("rpl_core", "ops_extended", "rpl_quantization", "rpl_gpu"):
             subprocess.run(["objcopy", "--weaken", o], check=True)
         objs.append(o)
     ours = sorted(glob.glob(os.path.join(build.OBJ_DIR, "*.o")))
@@ -77,7 +77,7 @@ def test_combined_library_keeps_the_rest_of_the_reference(tmp_path, lib):
     subprocess.run([build._nvcc(), "-shared", "-o", out] + objs + ours + ["-cudart", "static", "-Xcompiler", "-fopenmp", "-lm"],
                    check=True, capture_output=True)
     L = C.CDLL(out)
-    for name in ("tensor_gemm", "linear_forward", "optimizer_adam_create", "rplb_minmax_f32", "quantized_linear_forward"):
+    for name in ("tensor_gemm", "linear_forward", "optimizer_adam_create", "rplb_minmax_f32", "quantized_linear_forward", "tensor_to_gpu"):
         assert hasattr(L, name), name
     # the INT8 entry point is this library's: it can report a CUDA error code
     L.rpl_cuda_last_error.restype = C.c_int

@@ -267,3 +267,56 @@ def test_quantized_linear_host_pipeline(cuda, lib, port):
         lib.tensor_free(p)
     lib.quantized_linear_free(layer)
     assert lib.rpl_cuda_last_error() == 0
+
+
+def test_tensor_to_gpu_mirrors(cuda, lib, port):
+    """The reference's accelerator hooks (include/rpl.h:105-108) on CUDA: a mirrored
+    tensor keeps its host block, the INT8 calls read the mirror and answer in device
+    memory, tensor_from_gpu brings the mirror back."""
+    assert lib.rpl_gpu_init()
+    rng = np.random.default_rng(43)
+    x = (rng.standard_normal((24, 1024)) * 2).astype(np.float32)
+    t = host_tensor(lib, x)
+    host_block = t.contents.data
+    lib.tensor_to_gpu(t)
+    assert t.contents.device == 1 and t.contents.gpu_buffer != 0 and t.contents.data == host_block
+    handle = t.contents.gpu_buffer
+    lib.tensor_to_gpu(t)                                   # a second call changes nothing
+    assert t.contents.gpu_buffer == handle
+
+    # The mirror is what is read: change the host block, results still follow x.
+    C.memset(host_block, 0, x.nbytes)
+    qs = lib.tensor_quantize_int8_symmetric(t)
+    wq, ws = port.quantize_symmetric(x)
+    assert lib.rplb_pointer_kind(qs.contents.data) == 2 and same(np.float32(qs.contents.scale), ws)
+    back = lib.tensor_dequantize_int8(qs)
+    hb = lib.tensor_download(back)
+    assert same(read_host(hb.contents.data, x.shape, np.float32), port.dequantize(wq, ws, 0))
+    mn, mx = C.c_float(), C.c_float()
+    lib.tensor_get_min_max(t, C.byref(mn), C.byref(mx))
+    assert (np.float32(mn.value), np.float32(mx.value)) == port.minmax_serial(x)
+    pc = lib.tensor_quantize_per_channel(t, 0)
+    assert lib.rplb_pointer_kind(pc.contents.data) == 2
+    lib.per_channel_quantized_tensor_free(pc)
+
+    # In-place ReLU works on the mirror; tensor_from_gpu fills the host block with it.
+    lib.tensor_relu_inplace(t)
+    assert not read_host(host_block, x.shape, np.float32).any()
+    lib.tensor_from_gpu(t)
+    assert same(read_host(host_block, x.shape, np.float32), np.where(x < 0, np.float32(0), x))
+    assert t.contents.device == 1 and t.contents.gpu_buffer == handle
+
+    # Handles are distinct per tensor and reusable after tensor_free.
+    u = host_tensor(lib, x[:2])
+    lib.tensor_to_gpu(u)
+    assert u.contents.gpu_buffer not in (0, handle)
+    for p in (u, t, hb, back):
+        lib.tensor_free(p)
+    lib.quantized_tensor_free(qs)
+    v = host_tensor(lib, x[:3])
+    lib.tensor_to_gpu(v)
+    lib.tensor_from_gpu(v)
+    assert same(read_host(v.contents.data, (3, 1024), np.float32), x[:3])
+    lib.tensor_free(v)
+    lib.rpl_gpu_shutdown()
+    assert lib.rpl_cuda_last_error() == 0
