@@ -52,6 +52,8 @@ def parse_args():
                          "-1 = choose: pipelined when a rank's GEMM is short enough for the quantize pass to matter)")
     ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 tcgen05 128x256 tiles, 4 CTA pair, 5 256x256 tiles per CTA)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
+    ap.add_argument("--gather", action="store_true",
+                    help="with N > 1 also time the all-gather of the fp32 column blocks into [M, N] on every rank (own line, not part of value)")
     return ap.parse_args()
 
 
@@ -420,6 +422,27 @@ def run_ours(a):
         per_rank = per_rank.reshape(1, 3)
     per_rank = [[round(float(v), 4) for v in row] for row in per_rank.cpu()]
 
+    # ---- optional: all-gather of the column blocks, timed on its own ----
+    gather = None
+    if a.gather and world > 1:
+        full = layer.gather(out)                            # warm-up: NCCL channels and buffers
+        del full
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        g0.record()
+        for _ in range(reps):
+            full = layer.gather(out)
+            del full
+        g1.record()
+        barrier()
+        tg = torch.tensor([g0.elapsed_time(g1) / reps], device=dev)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        received = float(M) * (N - count) * 4
+        gather = {"ms": float(tg.item()), "received_bytes_per_rank": received,
+                  "GB/s_per_rank_in": received / (float(tg.item()) * 1e-3) / 1e9,
+                  "what": "NCCL all-gather of fp32 [M, N/G] blocks plus unpack into row-major [M, N] on every rank"}
+
     # ---- end to end through host buffers ----
     e2e = None
     if not a.no_e2e:
@@ -515,6 +538,8 @@ def run_ours(a):
                      "frac_of_nominal_4500": achieved / 4500.0},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
     }
+    if gather is not None:
+        line["gather"] = gather
     if world == 1 and not a.no_sweep:
         line["quantize_sweep"] = quantize_sweep(torch, D, dev, peaks)
     if world == 1 and not a.no_cpu:

@@ -44,8 +44,11 @@ def gather_columns(block, n_total, world=None, group=None, align=256):
         send = block.new_zeros((M, widest))
         send[:, : block.shape[1]] = block
     send = send.contiguous()
-    recv = [torch.empty_like(send) for _ in range(world)]
-    dist.all_gather(recv, send, group=group)
+    # One [world * M, widest] landing buffer: the collective writes it in place,
+    # with no per-rank list to flatten.
+    recv = send.new_empty((world * M, widest))
+    dist.all_gather_into_tensor(recv, send, group=group)
+    recv = recv.view(world, M, widest)
     out = block.new_empty((M, n_total))
     for r in range(world):
         b, c = shard_range(n_total, world, r, align)
