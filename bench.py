@@ -443,6 +443,34 @@ def run_ours(a):
                   "GB/s_per_rank_in": received / (float(tg.item()) * 1e-3) / 1e9,
                   "what": "NCCL all-gather of fp32 [M, N/G] blocks plus unpack into row-major [M, N] on every rank"}
 
+    # ---- optional: the same step with the gather fused into the GEMM epilogue ----
+    if a.gather and world > 1:
+        from rpl_b200.sharded import PeerOutput
+        shared = PeerOutput(M, N, dev)
+        for _ in range(2):
+            layer.forward_gathered(A, shared)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(a.steps):
+            layer.forward_gathered(A, shared)
+        f1.record()
+        barrier()
+        tf = torch.tensor([f0.elapsed_time(f1) / a.steps], device=dev)
+        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+        same_block = bool(torch.equal(shared.local[:256, begin:begin + count], out[:256]))
+        other = (rank + 1) % world
+        ob, oc = shard_range(N, world, other, 256)
+        probe = out[:256, :min(oc, 1024)].contiguous()       # the neighbour's first rows and columns, for a cross-check
+        probes = [torch.empty_like(probe) for _ in range(world)]
+        dist.all_gather(probes, probe)
+        same_remote = bool(torch.equal(shared.local[:256, ob:ob + min(oc, 1024)], probes[other]))
+        gather["fused"] = {"ms_per_step": float(tf.item()), "value": ops_total / (float(tf.item()) * 1e-3) / 1e12, "unit": UNIT,
+                           "what": "quantize + GEMM whose epilogue stores every tile into all ranks' [M, N] buffers over NVLink (peer stores), fences included",
+                           "matches_sharded_run": same_block and same_remote}
+        shared.close()
+        del shared
+
     # ---- end to end through host buffers ----
     e2e = None
     if not a.no_e2e:

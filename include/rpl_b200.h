@@ -140,6 +140,17 @@ int  rplb_stream_wait_event(void* stream, void* event);
 /* 0 = ordinary host memory, 1 = page-locked host, 2 = device, 3 = managed */
 int  rplb_pointer_kind(const void* p);
 
+/* One process per GPU on one node: a block from rplb_malloc is shared by
+ * exporting a handle of RPLB_IPC_HANDLE_BYTES bytes (sent to the other
+ * processes by any means), which they open to get an address of the same
+ * memory in their own address space; peer access between the two GPUs is
+ * switched on as needed.  Close before the owner frees the block.  No
+ * counterpart in the reference (single process, no accelerator memory). */
+#define RPLB_IPC_HANDLE_BYTES 64
+int  rplb_ipc_export(const void* dptr, void* handle);
+int  rplb_ipc_open(const void* handle, void** dptr);
+int  rplb_ipc_close(void* dptr);
+
 /* ------------------------------------------------------------------------
  * Quantization parameters as the reduction kernel leaves them on the device.
  * ---------------------------------------------------------------------- */
@@ -238,6 +249,23 @@ int  rplb_linear_i8_dequant_f32(const int8_t* x, const int8_t* w, float* out,
                                 uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
                                 const float* a_scale, const float* w_scales, const float* bias,
                                 int relu, void* stream);
+
+/* The same call for an output whose column blocks are computed on different
+ * GPUs and wanted whole on each of them: besides `out`, the values are stored
+ * at the same [m, n] offsets (row stride ldo) in n_peers further buffers
+ * (at most 7), normally the other ranks' [M, N_total] outputs opened with
+ * rplb_ipc_open, every pointer already advanced to this rank's first column.
+ * peer_out is a host array.  The exchange rides in the GEMM's epilogue as plain
+ * stores over NVLink; no gather pass follows.  The caller orders the ranks:
+ * nobody may still read a destination when the call starts, and a rank may
+ * read its own buffer only after every rank's call has completed (a barrier
+ * on the streams, e.g. an NCCL all-reduce of one word).  Needs K % 16 == 0
+ * and 16-byte aligned x and w; other shapes are refused, not emulated.  No
+ * counterpart in the reference (single device). */
+int  rplb_linear_i8_dequant_f32_peers(const int8_t* x, const int8_t* w, float* out,
+                                      uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                                      const float* a_scale, const float* w_scales, const float* bias,
+                                      int relu, float* const* peer_out, int n_peers, void* stream);
 
 /* The same call that also reports what the next layer's per-tensor quantizer
  * needs, so that layer can skip its min/max pass over the fp32 output (no

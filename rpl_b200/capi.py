@@ -95,6 +95,9 @@ SIGNATURES = {
     "rplb_event_record": ("rc", [_vp, _vp]),
     "rplb_stream_wait_event": ("rc", [_vp, _vp]),
     "rplb_pointer_kind": (C.c_int, [_vp]),
+    "rplb_ipc_export": ("rc", [_vp, _vp]),
+    "rplb_ipc_open": ("rc", [_vp, C.POINTER(C.c_void_p)]),
+    "rplb_ipc_close": ("rc", [_vp]),
     "rplb_minmax_f32": ("rc", [_vp, _u64, _vp, _vp]),
     "rplb_minmax_f32_static": ("rc", [_vp, _u64, _vp, _vp]),
     "rplb_quantize_f32_i8": ("rc", [_vp, _vp, _u64, _f, _i, _vp]),
@@ -108,6 +111,8 @@ SIGNATURES = {
     "rplb_linear_i8_i32": ("rc", [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "rplb_gemm_i8_requant_i32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _f, _f, _f, _i, _i, _vp]),
     "rplb_linear_i8_dequant_f32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp]),
+    "rplb_linear_i8_dequant_f32_peers": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int,
+                                                C.POINTER(C.c_void_p), C.c_int, _vp]),
     "rplb_linear_i8_dequant_f32_absmax": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
     "rplb_linear_i8_requant_i8": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _i, _vp]),
     "rplb_gemm_backend": (C.c_int, [C.c_int]),

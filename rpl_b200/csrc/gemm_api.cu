@@ -208,6 +208,32 @@ int rplb_linear_i8_dequant_f32_absmax(const int8_t* x, const int8_t* w, float* o
     return 0;
 }
 
+int rplb_linear_i8_dequant_f32_peers(const int8_t* x, const int8_t* w, float* out, uint64_t M, uint64_t K, uint64_t N,
+                                     uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
+                                     int relu, float* const* peer_out, int n_peers, void* stream) {
+    const char* who = "rplb_linear_i8_dequant_f32_peers";
+    if (!a_scale || !w_scales) return fail(RPLB_E_BAD_ARG, "%s: null scale pointer", who);
+    if (n_peers < 0 || n_peers > kMaxPeers) return fail(RPLB_E_BAD_ARG, "%s: %d peers (at most %d)", who, n_peers, kMaxPeers);
+    if (n_peers > 0 && !peer_out) return fail(RPLB_E_BAD_ARG, "%s: null peer list", who);
+    GemmProblem p = {};
+    p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+    p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
+    p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu;
+    for (int i = 0; i < n_peers; i++) {
+        if (!peer_out[i]) return fail(RPLB_E_BAD_ARG, "%s: peer destination %d is null", who, i);
+        p.peer_out[i] = peer_out[i];
+    }
+    p.n_peers = n_peers;
+    if (n_peers == 0) return run_gemm(p, as_stream(stream));
+    if (M == 0 || N == 0) return 0;
+    if (!x || !w || !out) return fail(RPLB_E_BAD_ARG, "%s: null pointer", who);
+    if (ldo < N) return fail(RPLB_E_BAD_ARG, "%s: output row stride %llu < N %llu", who, (unsigned long long)ldo, (unsigned long long)N);
+    // Only the tensor-core kernel stores to peer destinations; there is no other route.
+    if (!gemm_tcgen05_supports(p))
+        return fail(RPLB_E_UNSUPPORTED, "%s: needs K %% 16 == 0 and 16-byte aligned x and w", who);
+    return gemm_tcgen05(p, as_stream(stream), 1);
+}
+
 int rplb_linear_i8_requant_i8(const int8_t* x, const int8_t* w, int8_t* out, uint64_t M, uint64_t K, uint64_t N,
                               uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
                               int relu, const float* out_scale, int32_t out_zero_point, void* stream) {

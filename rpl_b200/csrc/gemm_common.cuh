@@ -12,6 +12,8 @@ enum EpilogueMode : int {
     EPI_DEQUANT_I8 = 3,   // the same fp32 value quantized straight to int8 with a given output scale / zero point
 };
 
+constexpr int kMaxPeers = 7;          // a node of 8 GPUs: this rank and seven others
+
 struct GemmProblem {
     const int8_t* A;      // [M,K] row-major
     const int8_t* B;      // b_is_kn ? [K,N] row-major : [N,K] row-major
@@ -35,6 +37,10 @@ struct GemmProblem {
     // EPI_DEQUANT_I8
     const float* out_scale;   // one float on the device
     int32_t out_zp;
+    // EPI_DEQUANT_F32 only: further [M, ldo] destinations that receive the same
+    // values as `out` (buffers of other GPUs mapped into this process).
+    int n_peers;
+    float* peer_out[kMaxPeers];
 };
 
 #ifdef __CUDACC__

@@ -262,6 +262,46 @@ __device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t
     }
 }
 
+// The fp32 chunk once more, for the other ranks' buffers.  A thread holds one
+// row, so a warp's store instruction touches 32 rows with 16 bytes each: fine
+// for local memory, where L2 merges the pieces, but over NVLink every piece
+// would travel as a packet of its own.  The chunk therefore goes through a
+// 32 x 32 (pitch 36) shared-memory tile of this warp and leaves with lanes along
+// the columns: each instruction writes four rows of 128 contiguous bytes.
+// All 32 lanes take part (rows beyond M are exchanged but not stored).
+constexpr int PEER_PITCH = 36;                                   // floats per staged row: 16-byte aligned, conflict-free
+constexpr size_t PEER_STAGE_BYTES = 4 * 32 * PEER_PITCH * sizeof(float);   // one tile per epilogue warp
+
+__device__ __forceinline__ void store_chunk_to_peers(const GemmProblem& p, const float (&v)[32], uint64_t m_base,
+                                                     uint64_t n_first, float* tile, int lane) {
+    const uint64_t n_left = p.N - n_first;
+    __syncwarp();                                                // the previous chunk has been read out
+    #pragma unroll
+    for (int c = 0; c < 32; c += 4)
+        *reinterpret_cast<float4*>(tile + lane * PEER_PITCH + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+    __syncwarp();
+    const int sub = lane >> 3, c4 = (lane & 7) * 4;              // four rows per instruction, eight lanes per row
+    for (int d = 0; d < p.n_peers; d++) {
+        float* base = p.peer_out[d] + n_first + c4;
+        #pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int row = it * 4 + sub;
+            const uint64_t mm = m_base + (uint64_t)row;
+            if (mm >= p.M) continue;
+            const float4 q = *reinterpret_cast<const float4*>(tile + row * PEER_PITCH + c4);
+            float* dst = base + mm * p.ldo;
+            if ((uint64_t)(c4 + 3) < n_left && (((uintptr_t)dst & 15) == 0)) {
+                *reinterpret_cast<float4*>(dst) = q;
+            } else {
+                if ((uint64_t)c4 < n_left) dst[0] = q.x;
+                if ((uint64_t)(c4 + 1) < n_left) dst[1] = q.y;
+                if ((uint64_t)(c4 + 2) < n_left) dst[2] = q.z;
+                if ((uint64_t)(c4 + 3) < n_left) dst[3] = q.w;
+            }
+        }
+    }
+}
+
 // Per-tile staging of the per-column epilogue inputs into this warp's shared-memory slots.
 template <int MODE>
 __device__ __forceinline__ void stage_columns(const GemmProblem& p, uint64_t n0, int lane, float* s_scales, float* s_aux) {
@@ -286,7 +326,7 @@ __device__ __forceinline__ void stage_columns(const GemmProblem& p, uint64_t n0,
 }
 
 // --------------------------------------------------------------------------- the kernel
-template <int MODE>
+template <int MODE, bool PEERS = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                   const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
@@ -406,6 +446,16 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
                 tc_wait_ld();
                 store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
+                if (PEERS && MODE == EPI_DEQUANT_F32) {
+                    // The same values again (recomputed: the local store keeps no copy), for the peers.
+                    float v[32];
+                    #pragma unroll
+                    for (int c = 0; c < 32; c++)
+                        v[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[chunk * 32 + c], p.bias_f32 != nullptr,
+                                           s_bias[chunk * 32 + c], p.relu != 0);
+                    float* tile = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + sizeof(TcShared)) + ew * 32 * PEER_PITCH;
+                    store_chunk_to_peers(p, v, m - (uint64_t)lane, n_first, tile, lane);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -929,14 +979,15 @@ int gemm_tcgen05_status(bool clear) {
     return v;
 }
 
-template <int MODE>
+template <int MODE, bool PEERS = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t tiles_m,
                      uint32_t tiles_n, uint32_t num_kb, int* status_dev, unsigned int grid, cudaStream_t st) {
     // Opt in to more than 48 KiB of dynamic shared memory.  The attribute is
     // per device, so it is set on every launch (a cheap host-side call).
-    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)TC_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_kernel)")) return rc;
-    gemm_i8_tc_kernel<MODE><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    const size_t smem = TC_SMEM_BYTES + (PEERS ? PEER_STAGE_BYTES : 0);      // the peers' staging tiles follow TcShared
+    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_kernel<MODE, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)smem), "cudaFuncSetAttribute(gemm_i8_tc_kernel)")) return rc;
+    gemm_i8_tc_kernel<MODE, PEERS><<<grid, TC_THREADS, smem, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
     return launched("gemm_i8_tc_kernel");
 }
 
@@ -1019,6 +1070,12 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     unsigned int sms = (unsigned int)sm_count();
     if (sms == 0) sms = 148;
     if (p.b_is_kn) variant = 1;          // only the 128 x 256 kernel reads B[K,N] in place
+    if (p.n_peers > 0) {
+        // Only the 128 x 256 kernel with the fp32 epilogue stores to further destinations.
+        if (p.mode != EPI_DEQUANT_F32 || p.b_is_kn || p.n_peers > kMaxPeers)
+            return fail(RPLB_E_UNSUPPORTED, "peer destinations need the fp32 epilogue, W as [N,K] and at most %d peers", kMaxPeers);
+        variant = 1;
+    }
     if (variant == 0) {
         // Measured on B200 (1000 W cap): un-throttled, the pair kernel keeps the
         // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster;
@@ -1062,7 +1119,9 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     switch (p.mode) {
         case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
         case EPI_REQUANT_I32: return launch_tc<EPI_REQUANT_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
-        case EPI_DEQUANT_F32: return launch_tc<EPI_DEQUANT_F32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+        case EPI_DEQUANT_F32:
+            if (p.n_peers > 0) return launch_tc<EPI_DEQUANT_F32, true>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+            return launch_tc<EPI_DEQUANT_F32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
         case EPI_DEQUANT_I8:  return launch_tc<EPI_DEQUANT_I8>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
     }
     return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);

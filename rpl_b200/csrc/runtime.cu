@@ -156,6 +156,30 @@ int rplb_stream_wait_event(void* stream, void* event) {
     return cuda_ok(cudaStreamWaitEvent(as_stream(stream), static_cast<cudaEvent_t>(event), 0), "cudaStreamWaitEvent");
 }
 
+// Sharing a device block between the processes of one node (one process per
+// GPU): the owner exports a 64-byte handle, the others open it and get an
+// address of the same memory in their own address space, with peer access
+// between the two GPUs switched on as needed.
+static_assert(sizeof(cudaIpcMemHandle_t) == RPLB_IPC_HANDLE_BYTES, "handle size");
+
+int rplb_ipc_export(const void* dptr, void* handle) {
+    if (!dptr || !handle) return fail(RPLB_E_BAD_ARG, "rplb_ipc_export: null pointer");
+    cudaIpcMemHandle_t h;
+    if (int rc = cuda_ok(cudaIpcGetMemHandle(&h, const_cast<void*>(dptr)), "cudaIpcGetMemHandle")) return rc;
+    memcpy(handle, &h, sizeof(h));
+    return 0;
+}
+
+int rplb_ipc_open(const void* handle, void** dptr) {
+    if (!handle || !dptr) return fail(RPLB_E_BAD_ARG, "rplb_ipc_open: null pointer");
+    *dptr = nullptr;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    return cuda_ok(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+
+int rplb_ipc_close(void* dptr) { return dptr ? cuda_ok(cudaIpcCloseMemHandle(dptr), "cudaIpcCloseMemHandle") : 0; }
+
 int rplb_pointer_kind(const void* p) {
     if (!p) return 0;
     cudaPointerAttributes a;

@@ -188,6 +188,30 @@ def linear_i8_dequant(x, w, a_scale, w_scales, bias=None, relu=False, out=None):
     return out
 
 
+def linear_i8_dequant_peers(x, w, a_scale, w_scales, out, peer_ptrs, bias=None, relu=False):
+    """``linear_i8_dequant`` whose values are also stored, at the same offsets and row
+    stride, into further buffers given by raw device addresses (``peer_ptrs``: other
+    ranks' outputs opened with ``rplb_ipc_open``, each advanced to this rank's first
+    column).  The caller orders the ranks around the call."""
+    import ctypes as C
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError("w must be [N, K] with K = %d" % K)
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out.dtype != torch.float32 or not out.is_cuda or out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("out must be a float32 CUDA [M,N] view with unit column stride")
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    ptrs = (C.c_void_p * max(1, len(peer_ptrs)))(*[int(q) for q in peer_ptrs])
+    capi.call("rplb_linear_i8_dequant_f32_peers", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
+              _p(bias), 1 if relu else 0, ptrs, len(peer_ptrs), _stream())
+    return out
+
+
 def linear_i8_dequant_absmax(x, w, a_scale, w_scales, bias=None, relu=False, out=None):
     """``linear_i8_dequant`` that also returns ``(absmax, next_scale)``: max |out| and
     absmax / 127, the per-tensor symmetric scale of ``out``, both one-element device

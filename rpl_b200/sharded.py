@@ -245,11 +245,95 @@ class ShardedQuantizedLinear:
         main.synchronize()
         return out_host
 
+    def forward_gathered(self, x, peer_output):
+        """``forward`` + ``gather`` in one pass: this rank's columns are written into
+        ``peer_output.local`` and into every other rank's buffer by the GEMM epilogue.
+        After the closing fence ``peer_output.local`` holds the whole ``[M, n_total]``."""
+        from . import device as D
+        xq, a_scale = self.quantize_activation(x)
+        begin, count = shard_range(self.n_total, self.world, self.rank, 256)
+        if count != self.wq.shape[0] or peer_output.n_total != self.n_total or peer_output.M != x.shape[0]:
+            raise ValueError("this rank's weight rows or the shared output do not match the column split")
+        peer_output.fence()                       # the previous contents are no longer read anywhere
+        if count:
+            block = peer_output.local[:, begin:begin + count]
+            D.linear_i8_dequant_peers(xq, self.wq, a_scale, self.w_scales, block,
+                                      peer_output.peer_block_ptrs(begin), bias=self.bias, relu=self.relu)
+        peer_output.fence()                       # every rank's stores have landed
+        return peer_output.local
+
     def gather(self, block, group=None):
         """Full ``[M, n_total]`` output on every rank (NCCL all-gather of column blocks)."""
         if self.world == 1:
             return block
         return gather_columns(block, self.n_total, self.world, group)
+
+
+class _RawBlock:
+    """A device block that torch can view without owning it."""
+
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+class PeerOutput:
+    """The whole ``[M, n_total]`` fp32 output on every rank, written by the GEMMs themselves.
+
+    Each rank allocates its ``[M, n_total]`` buffer with the library's allocator,
+    exports it, and opens the buffers of the other ranks of the node
+    (``rplb_ipc_export`` / ``rplb_ipc_open``; the handles travel through the process
+    group).  ``ShardedQuantizedLinear.forward_gathered`` then stores every output tile
+    into all of them from the GEMM's epilogue, so no gather pass follows the GEMM.
+    """
+
+    def __init__(self, M, n_total, device, group=None):
+        import ctypes as C
+
+        from . import capi
+        self.M, self.n_total, self.group = int(M), int(n_total), group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._capi = capi
+        base = C.c_void_p()
+        capi.call("rplb_malloc", C.byref(base), self.M * self.n_total * 4)
+        self.base = int(base.value)
+        self.local = torch.as_tensor(_RawBlock(self.base, (self.M, self.n_total)), device=device)
+        handle = (C.c_char * 64)()
+        capi.call("rplb_ipc_export", self.base, handle)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.peer_bases = {}
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                continue
+            opened = C.c_void_p()
+            capi.call("rplb_ipc_open", (C.c_char * 64).from_buffer_copy(h), C.byref(opened))
+            self.peer_bases[r] = int(opened.value)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def peer_block_ptrs(self, begin):
+        """Addresses of column ``begin`` of row 0 in every other rank's buffer."""
+        return [b + int(begin) * 4 for _, b in sorted(self.peer_bases.items())]
+
+    def fence(self):
+        """Orders the ranks on their streams: everything a rank enqueued before the
+        fence has completed on every rank before anything enqueued after it starts."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self):
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        for b in self.peer_bases.values():
+            self._capi.call("rplb_ipc_close", b)
+        self.peer_bases = {}
+        if dist.is_initialized():
+            dist.barrier(group=self.group)          # nobody frees while a peer still has the block open
+        self.local = None
+        if self.base:
+            self._capi.call("rplb_free", self.base)
+            self.base = 0
 
 
 class HostPipeline:
