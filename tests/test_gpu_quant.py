@@ -100,7 +100,10 @@ def test_misaligned_views_take_the_scalar_path(cuda, lib, port):
 
 
 @pytest.mark.parametrize("shape", [(1, 4), (10, 128), (128, 784), (7, 1031), (64, 4096), (5, 8192), (3, 8196),
-                                   (2, 40000), (300, 12), (4, 1 << 18)])
+                                   (2, 40000), (300, 12), (4, 1 << 18),
+                                   # long rows (the two-pass kernel), ragged lengths included
+                                   (5, 16384), (300, 8200), (3, 20000), (4, 65536), (40, 65540), (2, 100000),
+                                   (37, 131072), (3, 262144), (2, 262148), (2, 300000)])
 def test_per_channel_shapes(cuda, lib, port, shape):
     from rpl_b200 import device as D
     rng = np.random.default_rng(shape[0] * 7919 + shape[1])
@@ -111,6 +114,24 @@ def test_per_channel_shapes(cuda, lib, port, shape):
     wq, wsc, wzp = port.quantize_per_channel(x, shape[0])
     assert same(host(sc), wsc) and same(host(zp), wzp) and same(host(q), wq)
     assert same(host(D.dequantize_per_channel(q, sc)), port.dequantize_per_channel(wq, wsc))
+
+
+@pytest.mark.parametrize("length", [16384, 32768, 65536, 131072, 262144])
+def test_per_channel_extreme_in_one_part_only(cuda, lib, port, length):
+    """Long rows: the value that sets a channel's scale sits at one place only, a
+    different one per row, next to a NaN that the min/max compares must skip."""
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(length)
+    rows = 19
+    x = (rng.standard_normal((rows, length)) * 0.5).astype(np.float32)
+    for r in range(rows):
+        pos = (r * (length // 16) + 13 * r) % length
+        x[r, pos] = np.float32((100.0 + r) * (-1.0 if r % 2 else 1.0))
+        x[r, (pos + length // 2) % length] = np.nan            # skipped by the min/max compares
+    x[5, :] = np.float32(-0.0)
+    q, sc, zp = D.quantize_per_channel(dev(x, cuda))
+    wq, wsc, wzp = port.quantize_per_channel(x, rows)
+    assert same(host(sc), wsc) and same(host(zp), wzp) and same(host(q), wq)
 
 
 def test_round_trip_and_idempotence_at_sweep_size(cuda, lib):
