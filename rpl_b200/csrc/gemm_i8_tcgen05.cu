@@ -305,21 +305,34 @@ __device__ __forceinline__ void store_chunk_to_peers(const GemmProblem& p, const
 // Per-tile staging of the per-column epilogue inputs into this warp's shared-memory slots.
 template <int MODE>
 __device__ __forceinline__ void stage_columns(const GemmProblem& p, uint64_t n0, int lane, float* s_scales, float* s_aux) {
+    // All loads are issued before the first store, so the warp (alone on its
+    // scheduler) waits for global memory once, not once per 32 columns.
     if (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) {
+        float sc[TILE_N / 32], bi[TILE_N / 32];
+        #pragma unroll
+        for (int j = 0; j < TILE_N / 32; j++) {
+            const uint64_t n = n0 + (uint64_t)(lane + 32 * j);
+            sc[j] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
+            bi[j] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
+        }
         __syncwarp();
-        for (int c = lane; c < TILE_N; c += 32) {
-            const uint64_t n = n0 + c;
-            s_scales[c] = n < p.N ? __ldg(p.w_scales + n) : 0.0f;
-            s_aux[c] = (p.bias_f32 && n < p.N) ? __ldg(p.bias_f32 + n) : 0.0f;
+        #pragma unroll
+        for (int j = 0; j < TILE_N / 32; j++) {
+            s_scales[lane + 32 * j] = sc[j];
+            s_aux[lane + 32 * j] = bi[j];
         }
         __syncwarp();
     } else if (MODE == EPI_REQUANT_I32) {
         if (p.b_col_sums) {
-            __syncwarp();
-            for (int c = lane; c < TILE_N; c += 32) {
-                const uint64_t n = n0 + c;
-                s_aux[c] = __int_as_float(n < p.N ? __ldg(p.b_col_sums + n) : 0);
+            int32_t cs[TILE_N / 32];
+            #pragma unroll
+            for (int j = 0; j < TILE_N / 32; j++) {
+                const uint64_t n = n0 + (uint64_t)(lane + 32 * j);
+                cs[j] = n < p.N ? __ldg(p.b_col_sums + n) : 0;
             }
+            __syncwarp();
+            #pragma unroll
+            for (int j = 0; j < TILE_N / 32; j++) s_aux[lane + 32 * j] = __int_as_float(cs[j]);
             __syncwarp();
         }
     }
@@ -426,13 +439,14 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
+        uint64_t staged_n0 = ~0ull;          // column block whose scales / bias / sums are in shared memory
         uint32_t acc = 0, acc_phase = 0;
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn, GROUP_M);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
             const uint64_t m = (uint64_t)tm * TILE_M + quarter * 32 + lane;
-            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -639,13 +653,14 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
+        uint64_t staged_n0 = ~0ull;          // column block whose scales / bias / sums are in shared memory
         uint32_t acc = 0, acc_phase = 0;
         for (uint32_t tile = pair; tile < total_tiles; tile += num_pairs) {
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn, PAIR_GROUP_M);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
             const uint64_t m = (uint64_t)tm * PAIR_TILE_M + cta * 128 + quarter * 32 + lane;
-            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -795,12 +810,13 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
+        uint64_t staged_n0 = ~0ull;
         uint32_t acc_phase = 0;
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
-            stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+            if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             bool ok = mbar_wait_bounded(&sh->acc_full, acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
