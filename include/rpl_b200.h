@@ -416,6 +416,14 @@ void    linear_int8_dequant(const QuantizedTensor* x, const PerChannelQuantizedT
 typedef struct QuantizedLinear QuantizedLinear;
 QuantizedLinear* quantized_linear_create(const Tensor* weight, const Tensor* bias);
 Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bool relu);
+/* Several layers over one input, as multi-head attention applies W_q, W_k, W_v
+ * to the same activation (src/rpl_attention.c:175-177): the activation is
+ * quantized once and every layer's GEMM reads that int8 copy.  All layers must
+ * have the same in_features.  outputs[i] receives a new Tensor
+ * [rows, out_features of layer i]; returns 0, or an error code with every
+ * outputs[i] NULL. */
+int     quantized_linear_forward_shared_input(QuantizedLinear* const* layers, uint32_t num_layers, const Tensor* input,
+                                              Tensor** outputs, bool relu);
 void    quantized_linear_free(QuantizedLinear* layer);
 /* A layer over int8 weight rows [out,in], per-row scales and an optional fp32 bias
  * that already live in device memory and remain the caller's. */

@@ -157,6 +157,7 @@ SIGNATURES = {
     "quantized_linear_free": (None, [_vp]),
     "quantized_linear_wrap": (_vp, [_vp, _vp, _vp, C.c_uint32, C.c_uint32]),
     "quantized_linear_submit_host": (C.c_int, [_vp, _vp, C.c_uint32, _vp, C.c_bool, _vp]),
+    "quantized_linear_forward_shared_input": (C.c_int, [C.POINTER(_vp), C.c_uint32, _TP, C.POINTER(_TP), C.c_bool]),
     "quantized_linear_drain": (C.c_int, [_vp]),
     "quantized_weights_save": (C.c_int, [C.c_char_p, C.POINTER(_PP), C.c_uint32]),
     "quantized_weights_load": (C.POINTER(_PP), [C.c_char_p, C.POINTER(C.c_uint32), C.c_bool]),

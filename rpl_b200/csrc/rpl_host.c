@@ -864,6 +864,59 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
     return out;
 }
 
+/* Several layers applied to the same input, the way multi-head attention
+ * applies W_q, W_k and W_v to one activation (src/rpl_attention.c:175-177):
+ * the activation is quantized once (into the first layer's buffer) and every
+ * layer's GEMM reads that int8 copy.  outputs[i] receives a new Tensor
+ * [rows, out_features of layer i]; 0 on success, else nothing is returned and
+ * every outputs[i] is NULL. */
+int quantized_linear_forward_shared_input(QuantizedLinear* const* layers, uint32_t num_layers, const Tensor* input,
+                                          Tensor** outputs, bool relu) {
+    const char* who = "quantized_linear_forward_shared_input";
+    if (!layers || !outputs || num_layers == 0 || !input) return RPLB_E_BAD_ARG;
+    for (uint32_t i = 0; i < num_layers; i++) outputs[i] = NULL;
+    for (uint32_t i = 0; i < num_layers; i++)
+        if (!layers[i] || layers[i]->in_features != layers[0]->in_features) return RPLB_E_BAD_ARG;
+    QuantizedLinear* first = layers[0];
+    if (input->dims < 1 || input->size % first->in_features != 0) return RPLB_E_BAD_ARG;
+    t_last_error = 0;
+    for (uint32_t i = 0; i < num_layers; i++)
+        if (quantized_linear_drain(layers[i]) != 0) return t_last_error ? t_last_error : RPLB_E_KERNEL;
+    const size_t K = first->in_features, M = input->size / K;
+    const float* src = tensor_data(input);
+    const int dev_in = on_device(src);
+    if (first->act_capacity < M * K) {
+        rplb_stream_sync(NULL);
+        rplb_free(first->act);
+        first->act = NULL;
+        first->act_capacity = 0;
+        void* a = NULL;
+        if (report(rplb_malloc(&a, M * K), who) != 0) return t_last_error;
+        first->act = (int8_t*)a;
+        first->act_capacity = M * K;
+    }
+    const float* x = (const float*)to_device(0, src, M * K * 4);
+    if (M * K && !x) return t_last_error ? t_last_error : RPLB_E_BAD_ARG;
+    int rc = report(rplb_quantize_symmetric_f32_i8(x, first->act, M * K, first->act_params, NULL), who);
+    for (uint32_t i = 0; rc == 0 && i < num_layers; i++) {
+        const size_t N = layers[i]->out_features;
+        uint32_t out_shape[2] = {(uint32_t)M, (uint32_t)N};
+        outputs[i] = dev_in ? tensor_create_device(2, out_shape) : tensor_create(2, out_shape, false);
+        if (!outputs[i]) { rc = RPLB_E_BAD_ARG; break; }
+        /* Host results pass through one staging block: finish each layer's copy before the next GEMM reuses it. */
+        float* o = dev_in ? outputs[i]->data : (float*)stage(3, M * N * 4);
+        if (!o) { rc = t_last_error ? t_last_error : RPLB_E_BAD_ARG; break; }
+        rc = report(rplb_linear_i8_dequant_f32(first->act, layers[i]->weight->data, o, M, K, N, N, &first->act_params->scale_sym,
+                                               layers[i]->weight->scales, layers[i]->bias, relu ? 1 : 0, NULL), who);
+        if (rc == 0 && !dev_in) rc = report(rplb_copy(outputs[i]->data, o, M * N * 4, NULL), who);
+    }
+    if (rc == 0) rc = finish(who);
+    if (rc != 0) {
+        for (uint32_t i = 0; i < num_layers; i++) { tensor_free(outputs[i]); outputs[i] = NULL; }
+    }
+    return rc;
+}
+
 /* A layer over int8 weight rows, scales and bias that already live in device
  * memory and stay the caller's (nothing is copied, nothing is freed by
  * quantized_linear_free). */

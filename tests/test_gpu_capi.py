@@ -320,3 +320,57 @@ def test_tensor_to_gpu_mirrors(cuda, lib, port):
     lib.tensor_free(v)
     lib.rpl_gpu_shutdown()
     assert lib.rpl_cuda_last_error() == 0
+
+
+def test_shared_input_forward_like_attention_projections(cuda, lib, port):
+    """quantized_linear_forward_shared_input: Q, K and V projections of one activation
+    (src/rpl_attention.c:175-177), the activation quantized once; host and device inputs."""
+    rng = np.random.default_rng(47)
+    M, K = 200, 256
+    widths = (256, 128, 384)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    Ws = [(rng.standard_normal((n, K)) * 0.05).astype(np.float32) for n in widths]
+    bs = [(rng.standard_normal(n) * 0.05).astype(np.float32) for n in widths]
+    tws, tbs = [host_tensor(lib, w) for w in Ws], [host_tensor(lib, b) for b in bs]
+    layers = [lib.quantized_linear_create(tw, tb) for tw, tb in zip(tws, tbs)]
+    assert all(layers)
+    arr = (C.c_void_p * 3)(*layers)
+    xq, s = port.quantize_symmetric(x)
+    wants = []
+    for w, b in zip(Ws, bs):
+        wq, ws, _ = port.quantize_per_channel(w, w.shape[0])
+        wants.append(port.linear_dequant(xq, wq, s, ws, b, relu=False))
+
+    th = host_tensor(lib, x)
+    outs = (C.POINTER(type(th.contents)) * 3)()
+    assert lib.quantized_linear_forward_shared_input(arr, 3, th, outs, False) == 0
+    for o, want, n in zip(outs, wants, widths):
+        assert o.contents.device == 0 and list(o.contents.shape[:2]) == [M, n]
+        assert same(read_host(o.contents.data, (M, n), np.float32), want)
+        lib.tensor_free(o)
+
+    td = lib.tensor_upload(th)
+    outs = (C.POINTER(type(th.contents)) * 3)()
+    assert lib.quantized_linear_forward_shared_input(arr, 3, td, outs, False) == 0
+    for o, want, n, layer in zip(outs, wants, widths, layers):
+        assert o.contents.device == 1
+        h = lib.tensor_download(o)
+        assert same(read_host(h.contents.data, (M, n), np.float32), want)
+        single = lib.quantized_linear_forward(layer, td, False)            # the one-layer call gives the same bits
+        hs = lib.tensor_download(single)
+        assert same(read_host(hs.contents.data, (M, n), np.float32), want)
+        for t in (o, h, single, hs):
+            lib.tensor_free(t)
+
+    # layers that do not share in_features are refused and nothing is returned
+    odd = host_tensor(lib, Ws[0][:, :128].copy())
+    lo = lib.quantized_linear_create(odd, None)
+    bad = (C.c_void_p * 2)(layers[0], lo)
+    outs2 = (C.POINTER(type(th.contents)) * 2)()
+    assert lib.quantized_linear_forward_shared_input(bad, 2, th, outs2, False) != 0 and not outs2[0] and not outs2[1]
+    lib.quantized_linear_free(lo)
+    for l in layers:
+        lib.quantized_linear_free(l)
+    for t in tws + tbs + [th, td, odd]:
+        lib.tensor_free(t)
+    assert lib.rpl_cuda_last_error() == 0
