@@ -541,8 +541,8 @@ def run_ours(a):
             dist.destroy_process_group()
         return
 
-    # DRAM traffic of the GEMM from the ncu capture at 16384 x 16384 x 8192
-    # (profiles/gemm_i8_tc_kernel_8192cubed.md): 6.99 B per output element at K = 8192.
+    # DRAM traffic of the GEMM from an ncu capture at 16384 x 16384 x 8192
+    # (dram read + write): 6.99 B per output element at K = 8192.
     gemm_launches_per_step = max(1, len(gemm_pairs) // max(a.steps, 1)) if a.overlap > 1 else 1
     traffic = 6.99 * M * count / gemm_launches_per_step if K == 8192 else None
     int8_peak = 2.0 * peaks["bf16_sustained"]

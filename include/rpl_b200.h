@@ -117,16 +117,38 @@ typedef struct {
 #define RPLB_E_TOO_LARGE    (-3)   /* size beyond what the entry point takes   */
 #define RPLB_E_KERNEL       (-4)   /* a kernel reported a bounded wait expired */
 #define RPLB_E_UNSUPPORTED  (-5)   /* shape the selected GEMM kernel can't run */
+#define RPLB_E_COMM         (-6)   /* NCCL could not be loaded, or a communicator call failed */
 
 const char* rplb_last_error(void);          /* text of this thread's last failure */
 int  rplb_device_count(void);               /* 0 when there is no usable device   */
 int  rplb_device_sm_count(void);            /* SMs of the current device           */
+int  rplb_set_device(int ordinal);          /* device of the calling thread's later calls (one process per GPU: its rank) */
 
 /* ------------------------------------------------------------------------
  * Memory and stream helpers, so that a C host needs no CUDA headers.
  * ---------------------------------------------------------------------- */
 int  rplb_malloc(void** dptr, size_t bytes);
 int  rplb_free(void* dptr);
+/* An application that manages device memory itself installs its allocator here
+ * (both functions, or NULL and NULL to go back to cudaMalloc / cudaFree);
+ * rplb_malloc, rplb_free and the library's scratch blocks then use it.  The
+ * functions return 0 on success; a non-zero code from alloc_fn is handed back
+ * to the caller of the entry point that needed the memory.  Install before the
+ * first allocation.  The reference allocates with posix_memalign and has no
+ * hook (src/rpl_core.c:33-43). */
+typedef int (*rplb_alloc_fn)(void** dptr, size_t bytes);
+typedef int (*rplb_free_fn)(void* dptr);
+int  rplb_set_allocator(rplb_alloc_fn alloc_fn, rplb_free_fn free_fn);
+/* Scratch memory of the library: one block per (device, stream), allocated on
+ * first use and grown (after a stream synchronize, by free + allocate) when a
+ * call needs more: min/max partial results, a transposed B, row and column
+ * sums.  A CUDA graph captured from rplb_* calls keeps the block's address, so
+ * reserve the largest size the stream will ever need before capturing; a call
+ * that would have to grow the block of a capturing stream fails with
+ * RPLB_E_UNSUPPORTED instead.  release frees the block of a stream that is
+ * about to be destroyed. */
+int  rplb_scratch_reserve(void* stream, size_t bytes);
+int  rplb_scratch_release(void* stream);
 int  rplb_host_alloc(void** hptr, size_t bytes);     /* page-locked host memory */
 int  rplb_host_free(void* hptr);
 int  rplb_copy(void* dst, const void* src, size_t bytes, void* stream);   /* any direction, async */
@@ -189,6 +211,16 @@ int  rplb_minmax_f32(const float* x, uint64_t n, rplb_qparams* params, void* str
 #define RPLB_STATIC_MINMAX_MAX_CTAS      1024u
 #define RPLB_STATIC_MINMAX_MAX_ELEMENTS  (1ull << 30)
 int  rplb_minmax_f32_static(const float* x, uint64_t n, rplb_qparams* params, void* stream);
+
+/* A tensor whose rows live on several GPUs (src/rpl_quantization.c:79-88 over
+ * a row-sharded activation): every GPU runs rplb_minmax_f32 on its rows,
+ * to_pair leaves (-min, max) in two device floats, the caller combines the
+ * pairs of all GPUs with a max-reduction (ncclAllReduce, op max), and from_pair
+ * derives all parameters from the combined pair with the statements
+ * rplb_minmax_f32 itself ends with, IEEE division included, so every GPU holds
+ * the scale a single GPU would have computed. */
+int  rplb_qparams_to_pair(const rplb_qparams* params, float* pair, void* stream);
+int  rplb_qparams_from_pair(const float* pair, rplb_qparams* params, void* stream);
 
 /* Replaces the loop of tensor_quantize_int8 (src/rpl_core.c:521-527):
  * q = clamp((int32)roundf(x/scale) + zp, -128, 127). */
@@ -267,6 +299,24 @@ int  rplb_linear_i8_dequant_f32_peers(const int8_t* x, const int8_t* w, float* o
                                       const float* a_scale, const float* w_scales, const float* bias,
                                       int relu, float* const* peer_out, int n_peers, void* stream);
 
+/* The same call for an activation whose rows are still arriving from other GPUs
+ * when the kernel starts (the consumer half of an all-gather fused into the
+ * GEMM).  row_block_ready: one 32-bit word in this GPU's memory per block of
+ * 128 rows of x; a block is complete once its word has reached `epoch`
+ * (compared modulo 2^32), which the sender writes after the rows (for example a
+ * peer copy of the rows followed by a peer copy of the words on the same
+ * stream).  Blocks [local_first_block, local_first_block + local_blocks) are
+ * complete at launch: the kernel starts with them, takes the other blocks in
+ * ascending order (wrapping round), and before the first load of each waits,
+ * for about a second at most, for its word; if the wait runs out the kernel
+ * returns and rplb_kernel_status reports 5.  Needs K % 16 == 0 and 16-byte
+ * aligned x and w.  No counterpart in the reference (single device). */
+int  rplb_linear_i8_dequant_f32_arriving(const int8_t* x, const int8_t* w, float* out,
+                                         uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                                         const float* a_scale, const float* w_scales, const float* bias,
+                                         int relu, const uint32_t* row_block_ready, uint32_t epoch,
+                                         uint32_t local_first_block, uint32_t local_blocks, void* stream);
+
 /* The same call that also reports what the next layer's per-tensor quantizer
  * needs, so that layer can skip its min/max pass over the fp32 output (no
  * counterpart in the reference, which always re-scans: src/rpl_quantization.c:79-85).
@@ -293,9 +343,13 @@ int  rplb_linear_i8_requant_i8(const int8_t* x, const int8_t* w, int8_t* out,
  * place.  (The fused entry point above applies it inside the GEMM epilogue.) */
 int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
 
-/* Status word of the tensor-core kernel: 0, or the code of the bounded wait
- * that expired (1 stage-free, 2 stage-loaded, 3 accumulator-free,
- * 4 accumulator-ready).  Readable at any time; clear != 0 resets it. */
+/* Status word of the tensor-core kernels launched by the calling host thread:
+ * 0, or the code of the bounded wait that expired (1 stage-free, 2 stage-loaded,
+ * 3 accumulator-free, 4 accumulator-ready, 5 rows from another GPU).  Every
+ * host thread has a word of its own, so a give-up is seen by the thread that
+ * launched the kernel (and refuses that thread's next GEMM until cleared).
+ * Readable at any time; clear != 0 resets it.  A kernel that gave up leaves
+ * its output incomplete: check after synchronising. */
 int  rplb_kernel_status(int clear);
 
 /* Exercises the give-up path of the tensor-core kernels without a GEMM: one
@@ -303,8 +357,11 @@ int  rplb_kernel_status(int clear);
  * records its code and returns.  0 = the kernel returned, the status word held
  * the expected code and has been cleared.  Never blocks longer than the limit. */
 int  rplb_selftest_bounded_wait(void* stream);
+/* The same give-up, but its code (99) is left in the calling thread's status
+ * word for rplb_kernel_status to find; synchronises the stream. */
+int  rplb_selftest_bounded_wait_keep(void* stream);
 
-/* Which contraction kernel the three calls above use: 0 = automatic (tcgen05
+/* Which contraction kernel the calling host thread's calls use: 0 = automatic (tcgen05
  * tensor-core kernel when the shape allows it, else the dp4a kernel),
  * 1 = dp4a kernel, 2 = tcgen05 kernel (RPLB_E_UNSUPPORTED if the shape does
  * not fit it), 3 = tcgen05 with one CTA per 128x256 tile, 4 = tcgen05 with a
@@ -312,6 +369,12 @@ int  rplb_selftest_bounded_wait(void* stream);
  * 256x256 tile (two accumulators); 2 picks between 3 and 4 by size.
  * Returns the previous setting.  All of them are CUDA kernels. */
 int  rplb_gemm_backend(int which);
+/* How the tensor-core kernels of the calling thread store four-byte outputs:
+ * 0 = 32 x 32 chunks through shared memory and a TMA tensor store when the
+ * output's base and row stride are multiples of 16 bytes (else from registers),
+ * 1 = always from registers, one row per thread.  Same values either way.
+ * Returns the previous setting. */
+int  rplb_gemm_epilogue(int which);
 
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t rplb_launch_count(void);
@@ -319,6 +382,66 @@ uint64_t rplb_launch_count(void);
 /* Output-column block of rank `rank` out of `world` when N columns are split
  * in multiples of `align`: begin and count in columns.  Host arithmetic only. */
 int  rplb_shard_range(uint64_t n, int world, int rank, uint64_t align, uint64_t* begin, uint64_t* count);
+
+/* ------------------------------------------------------------------------
+ * The quantized Linear layer over the GPUs of one node, one process per GPU:
+ * the multi-GPU form of tensor_quantize_int8_symmetric + linear_int8
+ * (src/rpl_quantization.c:77-91, :314-353; the reference is single-device).
+ * Output columns (weight rows) and activation rows are both split over the
+ * ranks: rplb_sharded_linear_columns / _rows give this rank's blocks (columns
+ * in multiples of 256, rows in multiples of 128, as rplb_shard_range deals
+ * them).  forward takes this rank's fp32 rows, agrees on the per-tensor scale
+ * with one max-all-reduce, quantizes the rows, sends them to the other ranks
+ * over NVLink while the GEMM already runs on the local rows, and writes this
+ * rank's column block of the fp32 output [rows, ldo].  Results are the bits a
+ * single GPU produces.  NCCL is loaded at run time (libnccl.so.2, or the file
+ * named by RPLB_NCCL_LIBRARY) and only when world > 1.
+ *
+ * create is a collective call: rank 0 obtains an id with rplb_nccl_unique_id
+ * and hands the 128 bytes to the other ranks by any means (or every rank passes
+ * an ncclComm_t it already has as nccl_comm); all ranks then call create with
+ * the same world, max_rows, in_features and out_features_total.  weight_rows
+ * [count, in_features], scales [count] and bias [count] (may be NULL) are this
+ * rank's rows, in device memory, and stay the caller's.  With world > 1
+ * in_features must be a multiple of 16.  forward, gather and free are
+ * collective too (every rank calls them in the same order).
+ * ---------------------------------------------------------------------- */
+#define RPLB_NCCL_ID_BYTES 128
+typedef struct rplb_sharded_linear rplb_sharded_linear;
+int  rplb_nccl_unique_id(void* id);
+int  rplb_sharded_linear_create(rplb_sharded_linear** layer, int rank, int world, const void* nccl_id, void* nccl_comm,
+                                uint64_t max_rows, uint64_t in_features, uint64_t out_features_total,
+                                const int8_t* weight_rows, const float* scales, const float* bias);
+void rplb_sharded_linear_free(rplb_sharded_linear* layer);
+int  rplb_sharded_linear_columns(const rplb_sharded_linear* layer, uint64_t* begin, uint64_t* count);
+int  rplb_sharded_linear_rows(const rplb_sharded_linear* layer, uint64_t rows, uint64_t* begin, uint64_t* count);
+/* x_local: this rank's rows of the [rows, in_features] activation, fp32, device.
+ * out: this rank's [rows, count] column block, row stride ldo >= count, device. */
+int  rplb_sharded_linear_forward(rplb_sharded_linear* layer, const float* x_local, uint64_t rows, float* out, uint64_t ldo,
+                                 int relu, void* stream);
+/* forward in its two halves, for callers that want to put something between
+ * them (a timing event, other work on the stream): quantize = scale agreement,
+ * quantization of the local rows and the start of their transfer; gemm = the
+ * contraction over all `rows` rows of the activation quantized last. */
+int  rplb_sharded_linear_quantize(rplb_sharded_linear* layer, const float* x_local, uint64_t rows, void* stream);
+int  rplb_sharded_linear_gemm(rplb_sharded_linear* layer, uint64_t rows, float* out, uint64_t ldo, int relu, void* stream);
+/* After a forward: the whole int8 activation [rows, in_features] as this rank
+ * holds it, and its scale (one device float).  Both stay the layer's. */
+int  rplb_sharded_linear_activation(const rplb_sharded_linear* layer, const int8_t** xq, const float** scale);
+/* The whole [rows, out_features_total] fp32 matrix on every rank from the
+ * column blocks (row stride ld): ncclAllGather plus an unpack pass. */
+int  rplb_sharded_linear_gather(rplb_sharded_linear* layer, const float* block, uint64_t ld, uint64_t rows, float* full,
+                                void* stream);
+/* forward on host buffers, enqueued and pipelined like
+ * quantized_linear_submit_host: x_local (this rank's rows) and out (this rank's
+ * [rows, count] block, row stride count) in host memory, page-locked for full
+ * PCIe speed.  Every rank uploads only its own rows.  The GEMM runs in
+ * row_blocks blocks (0 = 8), each downloaded while the next computes; the
+ * upload of call n+1 overlaps the download of call n.  drain waits for all
+ * queued calls of this rank. */
+int  rplb_sharded_linear_submit_host(rplb_sharded_linear* layer, const float* x_local, uint64_t rows, float* out, int relu,
+                                     int row_blocks, void* compute_stream);
+int  rplb_sharded_linear_drain(rplb_sharded_linear* layer);
 
 /* ------------------------------------------------------------------------
  * The reference's exported names for the path.  Same signatures, ownership
@@ -378,6 +501,19 @@ void    calibrator_free(QuantizationCalibrator* cal);
 /* src/rpl_quantization.c:278-307 (per_channel is accepted and ignored, as there) */
 QuantizedModel* model_quantize(Tensor** parameters, uint32_t num_params, bool per_channel);
 void    quantized_model_free(QuantizedModel* qm);
+/* What model_quantize's per_channel flag announces and the reference leaves as
+ * a TODO (src/rpl_quantization.c:286-292); model_quantize itself keeps ignoring
+ * the flag, as the reference does.  Parameters with dims >= 2 are quantized per
+ * row of shape[0] (tensor_quantize_per_channel, axis 0), the others with one
+ * scale for the whole tensor (a single channel). */
+typedef struct {
+    Tensor**                    fp32_params;
+    PerChannelQuantizedTensor** int8_params;
+    uint32_t                    num_params;
+    bool                        is_quantized;
+} PerChannelQuantizedModel;
+PerChannelQuantizedModel* model_quantize_per_channel(Tensor** parameters, uint32_t num_params);
+void    per_channel_quantized_model_free(PerChannelQuantizedModel* qm);
 /* include/rpl.h:123, src/rpl_core.c:223-262 (ReLU between quantized layers) */
 void    tensor_relu_inplace(Tensor* t);
 

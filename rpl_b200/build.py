@@ -18,7 +18,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(LIB_DIR, "obj")
 LIB_PATH = os.path.join(LIB_DIR, "librpl.so")
 
-CU_SOURCES = ["runtime.cu", "quant_kernels.cu", "gemm_i8_simt.cu", "gemm_i8_tcgen05.cu", "gemm_api.cu"]
+CU_SOURCES = ["runtime.cu", "quant_kernels.cu", "gemm_i8_simt.cu", "gemm_i8_tcgen05.cu", "gemm_api.cu", "sharded.cu"]
 C_SOURCES = ["rpl_host.c"]
 HEADERS = ["common.cuh", "gemm_common.cuh"]
 
@@ -71,7 +71,7 @@ def build(force=False, verbose=False, extra_nvcc=()):
         objs.append(o)
     if force or _stale(LIB_PATH, objs):
         # The CUDA runtime is linked statically so the library stands alone.
-        _run([_nvcc(), "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-Xlinker", "--no-undefined", "-lm"],
+        _run([_nvcc(), "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-Xlinker", "--no-undefined", "-lm", "-ldl"],
              verbose)
     return LIB_PATH
 

@@ -16,7 +16,10 @@ f32p = C.POINTER(C.c_float)
 i8p = C.POINTER(C.c_int8)
 i32p = C.POINTER(C.c_int32)
 
-RPLB_E_NO_DEVICE, RPLB_E_BAD_ARG, RPLB_E_TOO_LARGE, RPLB_E_KERNEL, RPLB_E_UNSUPPORTED = -1, -2, -3, -4, -5
+RPLB_E_NO_DEVICE, RPLB_E_BAD_ARG, RPLB_E_TOO_LARGE, RPLB_E_KERNEL, RPLB_E_UNSUPPORTED, RPLB_E_COMM = -1, -2, -3, -4, -5, -6
+RPLB_NCCL_ID_BYTES = 128
+ALLOC_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_void_p), C.c_size_t)
+FREE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
 
 
 class RplError(RuntimeError):
@@ -65,6 +68,12 @@ class QuantizedModel(C.Structure):
                 ("num_params", C.c_uint32), ("is_quantized", C.c_bool)]
 
 
+class PerChannelQuantizedModel(C.Structure):
+    """``PerChannelQuantizedModel``: what ``model_quantize_per_channel`` returns."""
+    _fields_ = [("fp32_params", C.POINTER(C.POINTER(Tensor))), ("int8_params", C.POINTER(C.POINTER(PerChannelQuantizedTensor))),
+                ("num_params", C.c_uint32), ("is_quantized", C.c_bool)]
+
+
 class QParams(C.Structure):
     """``rplb_qparams``: what the min/max kernel leaves on the device (32 bytes)."""
     _fields_ = [("min_val", C.c_float), ("max_val", C.c_float), ("scale_sym", C.c_float),
@@ -81,9 +90,13 @@ SIGNATURES = {
     "rplb_last_error": (C.c_char_p, []),
     "rplb_device_count": (C.c_int, []),
     "rplb_device_sm_count": (C.c_int, []),
+    "rplb_set_device": ("rc", [C.c_int]),
     "rplb_launch_count": (C.c_uint64, []),
     "rplb_malloc": ("rc", [C.POINTER(_vp), _sz]),
     "rplb_free": ("rc", [_vp]),
+    "rplb_set_allocator": ("rc", [ALLOC_FN, FREE_FN]),
+    "rplb_scratch_reserve": ("rc", [_vp, _sz]),
+    "rplb_scratch_release": ("rc", [_vp]),
     "rplb_host_alloc": ("rc", [C.POINTER(_vp), _sz]),
     "rplb_host_free": ("rc", [_vp]),
     "rplb_copy": ("rc", [_vp, _vp, _sz, _vp]),
@@ -100,6 +113,8 @@ SIGNATURES = {
     "rplb_ipc_close": ("rc", [_vp]),
     "rplb_minmax_f32": ("rc", [_vp, _u64, _vp, _vp]),
     "rplb_minmax_f32_static": ("rc", [_vp, _u64, _vp, _vp]),
+    "rplb_qparams_to_pair": ("rc", [_vp, _vp, _vp]),
+    "rplb_qparams_from_pair": ("rc", [_vp, _vp, _vp]),
     "rplb_quantize_f32_i8": ("rc", [_vp, _vp, _u64, _f, _i, _vp]),
     "rplb_quantize_f32_i8_dev": ("rc", [_vp, _vp, _u64, _vp, _vp, _vp]),
     "rplb_quantize_symmetric_f32_i8": ("rc", [_vp, _vp, _u64, _vp, _vp]),
@@ -113,9 +128,25 @@ SIGNATURES = {
     "rplb_linear_i8_dequant_f32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp]),
     "rplb_linear_i8_dequant_f32_peers": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int,
                                                 C.POINTER(C.c_void_p), C.c_int, _vp]),
+    "rplb_linear_i8_dequant_f32_arriving": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int,
+                                                   _vp, C.c_uint32, C.c_uint32, C.c_uint32, _vp]),
     "rplb_linear_i8_dequant_f32_absmax": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
     "rplb_linear_i8_requant_i8": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _i, _vp]),
     "rplb_gemm_backend": (C.c_int, [C.c_int]),
+    "rplb_gemm_epilogue": (C.c_int, [C.c_int]),
+    "rplb_selftest_bounded_wait_keep": ("rc", [_vp]),
+    "rplb_nccl_unique_id": ("rc", [_vp]),
+    "rplb_sharded_linear_create": ("rc", [C.POINTER(_vp), C.c_int, C.c_int, _vp, _vp, _u64, _u64, _u64, _vp, _vp, _vp]),
+    "rplb_sharded_linear_free": (None, [_vp]),
+    "rplb_sharded_linear_columns": ("rc", [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
+    "rplb_sharded_linear_rows": ("rc", [_vp, _u64, C.POINTER(_u64), C.POINTER(_u64)]),
+    "rplb_sharded_linear_forward": ("rc", [_vp, _vp, _u64, _vp, _u64, C.c_int, _vp]),
+    "rplb_sharded_linear_quantize": ("rc", [_vp, _vp, _u64, _vp]),
+    "rplb_sharded_linear_gemm": ("rc", [_vp, _u64, _vp, _u64, C.c_int, _vp]),
+    "rplb_sharded_linear_activation": ("rc", [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "rplb_sharded_linear_gather": ("rc", [_vp, _vp, _u64, _u64, _vp, _vp]),
+    "rplb_sharded_linear_submit_host": ("rc", [_vp, _vp, _u64, _vp, C.c_int, C.c_int, _vp]),
+    "rplb_sharded_linear_drain": ("rc", [_vp]),
     "rplb_kernel_status": (C.c_int, [C.c_int]),
     "rplb_selftest_bounded_wait": ("rc", [_vp]),
     "rplb_shard_range": ("rc", [_u64, C.c_int, C.c_int, _u64, C.POINTER(_u64), C.POINTER(_u64)]),
@@ -145,6 +176,8 @@ SIGNATURES = {
     "calibrator_free": (None, [_CP]),
     "model_quantize": (_MP, [C.POINTER(_TP), C.c_uint32, C.c_bool]),
     "quantized_model_free": (None, [_MP]),
+    "model_quantize_per_channel": (_vp, [C.POINTER(_TP), C.c_uint32]),
+    "per_channel_quantized_model_free": (None, [_vp]),
     "tensor_relu_inplace": (None, [_TP]),
     "rpl_cuda_last_error": (C.c_int, []),
     "tensor_create_device": (_TP, [C.c_uint32, C.POINTER(C.c_uint32)]),

@@ -30,6 +30,10 @@ int scratch_for(cudaStream_t stream, size_t bytes, Scratch* out);
 
 int sm_count();              // SMs of the current device (cached per device)
 
+// The device allocator in use (cudaMalloc / cudaFree, or what rplb_set_allocator installed).
+int device_alloc(void** p, size_t bytes, const char* what);
+int device_free(void* p);
+
 static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // ---------------------------------------------------------------------------

@@ -8,8 +8,15 @@ namespace rplb {
 
 int gemm_tcgen05_status(bool clear);     // gemm_i8_tcgen05.cu
 int bounded_wait_selftest(cudaStream_t st);
+int bounded_wait_leave_status(cudaStream_t st);
 
-static std::atomic<int> g_backend{0};    // 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA
+// Per host thread: 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA
+static thread_local int t_backend = 0;
+int thread_gemm_backend(int which) {
+    const int prev = t_backend;
+    if (which >= 0 && which <= 5) t_backend = which;
+    return prev;
+}
 
 // Below this many multiply-accumulates the persistent tensor-core kernel has
 // no advantage over the dp4a kernel (one tile is 128 x 256 outputs).
@@ -83,14 +90,14 @@ static int launch_row_sums(const int8_t* X, int32_t* sums, uint64_t rows, uint64
     return launched("row_sums_i8_kernel");
 }
 
-static int run_gemm(GemmProblem p, cudaStream_t st) {
+int run_gemm(GemmProblem p, cudaStream_t st) {
     if (p.M == 0 || p.N == 0) return 0;
     // An operand with no elements (K = 0) may legitimately be a null pointer.
     if ((!p.A || !p.B) && p.K) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null input pointer");
     if (!p.out) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: null output pointer");
     if (p.ldo < p.N) return fail(RPLB_E_BAD_ARG, "INT8 GEMM: output row stride %llu < N %llu",
                                  (unsigned long long)p.ldo, (unsigned long long)p.N);
-    const int backend = g_backend.load(std::memory_order_relaxed);
+    const int backend = t_backend;
     if (backend == 1) return gemm_simt(p, st);
 
     GemmProblem q = p;
@@ -153,10 +160,11 @@ using namespace rplb;
 
 extern "C" {
 
-int rplb_gemm_backend(int which) {
-    if (which < 0 || which > 5) return g_backend.load();
-    return g_backend.exchange(which);
-}
+int rplb_gemm_backend(int which) { return thread_gemm_backend(which); }
+
+int rplb_gemm_epilogue(int which) { return thread_gemm_epilogue(which); }
+
+int rplb_selftest_bounded_wait_keep(void* stream) { return bounded_wait_leave_status(as_stream(stream)); }
 
 int rplb_kernel_status(int clear) { return gemm_tcgen05_status(clear != 0); }
 
@@ -229,6 +237,27 @@ int rplb_linear_i8_dequant_f32_peers(const int8_t* x, const int8_t* w, float* ou
     if (!x || !w || !out) return fail(RPLB_E_BAD_ARG, "%s: null pointer", who);
     if (ldo < N) return fail(RPLB_E_BAD_ARG, "%s: output row stride %llu < N %llu", who, (unsigned long long)ldo, (unsigned long long)N);
     // Only the tensor-core kernel stores to peer destinations; there is no other route.
+    if (!gemm_tcgen05_supports(p))
+        return fail(RPLB_E_UNSUPPORTED, "%s: needs K %% 16 == 0 and 16-byte aligned x and w", who);
+    return gemm_tcgen05(p, as_stream(stream), 1);
+}
+
+int rplb_linear_i8_dequant_f32_arriving(const int8_t* x, const int8_t* w, float* out, uint64_t M, uint64_t K, uint64_t N,
+                                        uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
+                                        int relu, const uint32_t* row_block_ready, uint32_t epoch,
+                                        uint32_t local_first_block, uint32_t local_blocks, void* stream) {
+    const char* who = "rplb_linear_i8_dequant_f32_arriving";
+    if (!a_scale || !w_scales) return fail(RPLB_E_BAD_ARG, "%s: null scale pointer", who);
+    if (M == 0 || N == 0) return 0;
+    if (!x || !w || !out) return fail(RPLB_E_BAD_ARG, "%s: null pointer", who);
+    if (!row_block_ready) return fail(RPLB_E_BAD_ARG, "%s: null arrival words", who);
+    if (ldo < N) return fail(RPLB_E_BAD_ARG, "%s: output row stride %llu < N %llu", who, (unsigned long long)ldo, (unsigned long long)N);
+    GemmProblem p = {};
+    p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+    p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
+    p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu;
+    p.a_ready = row_block_ready; p.a_epoch = epoch; p.a_local_first = local_first_block; p.a_local_count = local_blocks;
+    // Only the tensor-core kernel waits for arriving rows; there is no other route.
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "%s: needs K %% 16 == 0 and 16-byte aligned x and w", who);
     return gemm_tcgen05(p, as_stream(stream), 1);

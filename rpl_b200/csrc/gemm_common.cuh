@@ -41,6 +41,15 @@ struct GemmProblem {
     // values as `out` (buffers of other GPUs mapped into this process).
     int n_peers;
     float* peer_out[kMaxPeers];
+    // Rows of A that other GPUs deliver while the kernel runs (tensor-core kernel
+    // with 128-row tiles only).  a_ready[t] belongs to rows [128 t, 128 t + 128):
+    // the block is in place once (int32)(a_ready[t] - a_epoch) >= 0.  Blocks
+    // [a_local_first, a_local_first + a_local_count) are in place at launch; the
+    // kernel starts with them and takes the others in ascending order, wrapping
+    // round.  a_ready == nullptr: all of A is in place at launch.
+    const uint32_t* a_ready;
+    uint32_t a_epoch;
+    uint32_t a_local_first, a_local_count;
 };
 
 #ifdef __CUDACC__
@@ -89,8 +98,14 @@ __device__ __forceinline__ void absmax_publish(float* dst, float running) {
 
 // Implemented in gemm_i8_simt.cu / gemm_i8_tcgen05.cu.
 int gemm_simt(const GemmProblem& p, cudaStream_t st);
-// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = a CTA pair (two SMs) per 256 x 256 tile.
+// variant: 0 = choose, 1 = one CTA per 128 x 256 tile, 2 = a CTA pair (two SMs) per 256 x 256 tile,
+// 3 = one CTA per 256 x 256 tile.
 int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant = 0);
+// Which contraction kernel and which store path this host thread's calls use (rplb_gemm_backend, rplb_gemm_epilogue).
+int thread_gemm_backend(int which);
+int thread_gemm_epilogue(int which);
+// Argument checks and choice of kernel for one contraction (gemm_api.cu).
+int run_gemm(GemmProblem p, cudaStream_t st);
 // True when the tensor-core kernel can take the problem as it stands.
 bool gemm_tcgen05_supports(const GemmProblem& p);
 

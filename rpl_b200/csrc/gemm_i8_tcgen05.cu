@@ -22,8 +22,18 @@
 //               256-column TMEM accumulators, and tcgen05.commit to hand stages
 //               back to the producer and finished accumulators to the epilogue.
 //   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, apply the
-//               epilogue in registers, store to global memory.  While they drain
-//               one accumulator the MMA warp fills the other.
+//               epilogue in registers, then hand the 32 x 32 chunk of four-byte
+//               results to the TMA unit through a swizzled shared-memory tile
+//               (cp.async.bulk.tensor store: whole 128-byte row segments leave the
+//               SM, ragged edges are clipped by the tensor map); outputs whose
+//               base or row stride is not a multiple of 16 bytes, and int8
+//               outputs, are stored from registers instead.  While the epilogue
+//               drains one accumulator the MMA warp fills the other.
+//
+// Rows of A may still be on their way from other GPUs when the kernel starts
+// (GemmProblem::a_ready): the producer then begins with the 128-row blocks that
+// are in place and, before the first load of any other block, waits (bounded)
+// until that block's arrival word carries the call's epoch.
 //
 // Every wait on an mbarrier is bounded: when the limit passes the waiter writes
 // a code to a status word in global memory and raises a CTA-wide abort flag,
@@ -31,6 +41,8 @@
 // host turns the status word into RPLB_E_KERNEL.
 #include "gemm_common.cuh"
 #include <cuda.h>
+#include <atomic>
+#include <cstring>
 #include <mutex>
 
 namespace rplb {
@@ -54,6 +66,9 @@ constexpr int PAIR_GROUP_M = 16;     // 256-row m-tiles per group (CTA-pair kern
 
 // Dynamic shared memory, after alignment to 1024 bytes:
 //   [kStages][A tile | W tile]   then the block below.
+constexpr uint32_t EPI_TILE_BYTES = 32 * 128;            // one epilogue warp's staging tile: 32 rows x 32 four-byte results
+constexpr uint32_t EPI_STAGE_BYTES = 4 * EPI_TILE_BYTES;  // four epilogue warps; follows the stage ring, so it is 1024-byte aligned
+
 struct __align__(16) TcShared {
     uint64_t full[kStages];          // producer -> MMA: stage loaded
     uint64_t empty[kStages];         // MMA -> producer: stage consumed
@@ -64,10 +79,10 @@ struct __align__(16) TcShared {
     float w_scales[4 * TILE_N];      // per-tile copies for the fp32 epilogue, one per epilogue warp
     float bias[4 * TILE_N];
 };
-constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)kStages * STAGE_BYTES + sizeof(TcShared);
+constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)kStages * STAGE_BYTES + EPI_STAGE_BYTES + sizeof(TcShared);
 
 // Status codes written to the status word when a wait gives up.
-enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4, TC_WAIT_SELFTEST = 99 };
+enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4, TC_WAIT_ROWS = 5, TC_WAIT_SELFTEST = 99 };
 
 // --------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -113,11 +128,54 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits until a 128-row block of A sent by another GPU is in place: its arrival
+// word must have reached the call's epoch (compared modulo 2^32).  Bounded like
+// the mbarrier waits; on success the TMA unit is fenced so that its loads see
+// what the acquire saw.
+__device__ __forceinline__ bool wait_rows_ready(const uint32_t* word, uint32_t epoch, volatile int* abort_flag, int* status) {
+    if ((int32_t)(ld_acquire_sys(word) - epoch) < 0) {
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while ((int32_t)(ld_acquire_sys(word) - epoch) < 0) {
+            __nanosleep(100);
+            if ((++spins & 63u) == 0) {
+                if (*abort_flag) return false;
+                if (clock64() - t0 > kWaitLimitCycles) {
+                    *abort_flag = 1;
+                    atomicCAS(status, 0, (int)TC_WAIT_ROWS);
+                    return false;
+                }
+            }
+        }
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    return true;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+
+// Store of a shared-memory tile through a tensor map (bulk async-group completion).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Every bulk store of this thread has finished reading its shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Every bulk store of this thread is complete.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the TMA unit.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -179,108 +237,39 @@ constexpr uint32_t kIdescI8BMn = kIdescI8 | (1u << 16);      // B operand MN-maj
 // Tile index -> (m-tile, n-tile): tiles are numbered so that CTAs running at the
 // same time cover GROUP_M consecutive m-tiles of a few n-tiles, which keeps the
 // set of A and W rows being streamed small enough to be served from L2.
-__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t& tm, uint32_t& tn, uint32_t group_m = GROUP_M) {
+// `rotate` shifts the m-tile numbering (modulo tiles_m) so that the walk starts at
+// that m-tile: used when the first rows of A in place are not rows 0...
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t& tm, uint32_t& tn,
+                                            uint32_t group_m = GROUP_M, uint32_t rotate = 0) {
     const uint32_t per_group = group_m * tiles_n;
     const uint32_t group = tile / per_group;
     const uint32_t first_m = group * group_m;
     const uint32_t rows = min(group_m, tiles_m - first_m);
     const uint32_t in_group = tile - group * per_group;
-    tm = first_m + in_group % rows;
+    tm = first_m + in_group % rows + rotate;
+    if (tm >= tiles_m) tm -= tiles_m;
     tn = in_group / rows;
 }
 
 // --------------------------------------------------------------------------- epilogue of one 32-column chunk
-// Thread = one output row m; r[0..31] = accumulators of columns n_first..n_first+31.
-// s_scales / s_aux: this warp's shared-memory copies of the per-column values of
-// the chunk (weight scales and bias for the fp32 modes; s_aux holds the column
-// sums, as int32 bit patterns, when gemm_int8 runs with zero points).
-template <int MODE>
-__device__ __forceinline__ void store_chunk(const GemmProblem& p, const uint32_t (&r)[32], uint64_t m, uint64_t n_first,
-                                            float a_scale, const float* s_scales, const float* s_aux,
-                                            const QuantConsts& oq, int32_t row_sum, float& absmax) {
-    if (m >= p.M) return;
-    const uint64_t n_left = p.N - n_first;          // caller guarantees n_first < N
-    const bool full = n_left >= 32;
-    if (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) {
-        const bool has_bias = p.bias_f32 != nullptr;
-        const bool relu = p.relu != 0;
-        float v[32];
-        #pragma unroll
-        for (int c = 0; c < 32; c++) v[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[c], has_bias, s_aux[c], relu);
-        if (p.absmax_out) {
-            #pragma unroll
-            for (int c = 0; c < 32; c++)
-                if (full || (uint64_t)c < n_left) absmax_fold(absmax, v[c]);
-        }
-        if (MODE == EPI_DEQUANT_F32) {
-            float* row = static_cast<float*>(p.out) + m * p.ldo + n_first;
-            if (full && (((uintptr_t)row & 15) == 0)) {
-                #pragma unroll
-                for (int c = 0; c < 32; c += 4) __stcs(reinterpret_cast<float4*>(row + c), make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]));
-            } else {
-                #pragma unroll
-                for (int c = 0; c < 32; c++)
-                    if ((uint64_t)c < n_left) row[c] = v[c];
-            }
-        } else {
-            int8_t* row = static_cast<int8_t*>(p.out) + m * p.ldo + n_first;
-            uint32_t w[8];
-            #pragma unroll
-            for (int c = 0; c < 8; c++) w[c] = quantize_quad_packed(make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]), oq);
-            if (full && (((uintptr_t)row & 15) == 0)) {
-                __stcs(reinterpret_cast<uint4*>(row), make_uint4(w[0], w[1], w[2], w[3]));
-                __stcs(reinterpret_cast<uint4*>(row + 16), make_uint4(w[4], w[5], w[6], w[7]));
-            } else {
-                #pragma unroll
-                for (int c = 0; c < 32; c++)
-                    if ((uint64_t)c < n_left) row[c] = (int8_t)((w[c >> 2] >> (8 * (c & 3))) & 0xff);
-            }
-        }
-    } else {
-        int32_t* row = static_cast<int32_t*>(p.out) + m * p.ldo + n_first;
-        int32_t v[32];
-        #pragma unroll
-        for (int c = 0; c < 32; c++) {
-            int32_t s = (int32_t)r[c];
-            if (MODE == EPI_RAW_I32) {
-                if (p.bias_i8 && (uint64_t)c < n_left) s = (int32_t)((uint32_t)s + (uint32_t)(int32_t)__ldg(p.bias_i8 + n_first + c));
-            } else {
-                if (p.a_row_sums) s = apply_zero_points(s, row_sum, __float_as_int(s_aux[c]), p.za, p.zb, (uint32_t)p.K);
-                s = requant_i32(s, p.sa, p.sb, p.sc);
-            }
-            v[c] = s;
-        }
-        if (full && (((uintptr_t)row & 15) == 0)) {
-            #pragma unroll
-            for (int c = 0; c < 32; c += 4)
-                __stcs(reinterpret_cast<int4*>(row + c), make_int4(v[c], v[c + 1], v[c + 2], v[c + 3]));
-        } else {
-            #pragma unroll
-            for (int c = 0; c < 32; c++)
-                if ((uint64_t)c < n_left) row[c] = v[c];
-        }
-    }
+// A warp's staging tile holds 32 rows of 128 bytes with the 128-byte swizzle the
+// tensor map of the output expects: the 16-byte piece j of row r lies at piece
+// j ^ (r & 7).  Lane = row, so the eight lanes of a quarter warp write eight
+// different pieces: no bank conflicts.
+__device__ __forceinline__ void stage_row_swizzled(uint8_t* tile, int row, const uint32_t (&w)[32]) {
+    #pragma unroll
+    for (int j = 0; j < 8; j++)
+        *reinterpret_cast<uint4*>(tile + row * 128 + ((j ^ (row & 7)) << 4)) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
 }
 
-// The fp32 chunk once more, for the other ranks' buffers.  A thread holds one
-// row, so a warp's store instruction touches 32 rows with 16 bytes each: fine
-// for local memory, where L2 merges the pieces, but over NVLink every piece
-// would travel as a packet of its own.  The chunk therefore goes through a
-// 32 x 32 (pitch 36) shared-memory tile of this warp and leaves with lanes along
-// the columns: each instruction writes four rows of 128 contiguous bytes.
-// All 32 lanes take part (rows beyond M are exchanged but not stored).
-constexpr int PEER_PITCH = 36;                                   // floats per staged row: 16-byte aligned, conflict-free
-constexpr size_t PEER_STAGE_BYTES = 4 * 32 * PEER_PITCH * sizeof(float);   // one tile per epilogue warp
-
-__device__ __forceinline__ void store_chunk_to_peers(const GemmProblem& p, const float (&v)[32], uint64_t m_base,
-                                                     uint64_t n_first, float* tile, int lane) {
+// The staged fp32 chunk once more, for the other ranks' buffers.  Read back with
+// lanes along the columns, so that each instruction writes four rows of 128
+// contiguous bytes: over NVLink a 16-byte piece per row would travel as a packet
+// of its own.  All 32 lanes take part (rows beyond M are read but not stored).
+__device__ __forceinline__ void store_tile_to_peers(const GemmProblem& p, const uint8_t* tile, uint64_t m_base,
+                                                    uint64_t n_first, int lane) {
     const uint64_t n_left = p.N - n_first;
-    __syncwarp();                                                // the previous chunk has been read out
-    #pragma unroll
-    for (int c = 0; c < 32; c += 4)
-        *reinterpret_cast<float4*>(tile + lane * PEER_PITCH + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-    __syncwarp();
-    const int sub = lane >> 3, c4 = (lane & 7) * 4;              // four rows per instruction, eight lanes per row
+    const int sub = lane >> 3, j = lane & 7, c4 = j * 4;         // four rows per instruction, eight lanes per row
     for (int d = 0; d < p.n_peers; d++) {
         float* base = p.peer_out[d] + n_first + c4;
         #pragma unroll
@@ -288,7 +277,7 @@ __device__ __forceinline__ void store_chunk_to_peers(const GemmProblem& p, const
             const int row = it * 4 + sub;
             const uint64_t mm = m_base + (uint64_t)row;
             if (mm >= p.M) continue;
-            const float4 q = *reinterpret_cast<const float4*>(tile + row * PEER_PITCH + c4);
+            const float4 q = *reinterpret_cast<const float4*>(tile + row * 128 + ((j ^ (row & 7)) << 4));
             float* dst = base + mm * p.ldo;
             if ((uint64_t)(c4 + 3) < n_left && (((uintptr_t)dst & 15) == 0)) {
                 *reinterpret_cast<float4*>(dst) = q;
@@ -300,6 +289,95 @@ __device__ __forceinline__ void store_chunk_to_peers(const GemmProblem& p, const
             }
         }
     }
+}
+
+// Lane = one output row (m_base + lane); r[0..31] = accumulators of columns
+// n_first..n_first+31.  s_scales / s_aux: this warp's shared-memory copies of the
+// per-column values of the chunk (weight scales and bias for the fp32 modes;
+// s_aux holds the column sums, as int32 bit patterns, when gemm_int8 runs with
+// zero points).  tile: this warp's staging tile; tma_out: the four-byte results
+// leave through map_out (whole warp takes part), otherwise each lane stores its row.
+template <int MODE, bool PEERS>
+__device__ __forceinline__ void epilogue_chunk(const GemmProblem& p, const CUtensorMap* map_out, bool tma_out, uint8_t* tile,
+                                               const uint32_t (&r)[32], uint64_t m_base, int lane, uint64_t n_first,
+                                               float a_scale, const float* s_scales, const float* s_aux,
+                                               const QuantConsts& oq, int32_t row_sum, float& absmax) {
+    const uint64_t m = m_base + (uint64_t)lane;
+    const bool row_ok = m < p.M;
+    const uint64_t n_left = p.N - n_first;          // caller guarantees n_first < N
+    const bool full = n_left >= 32;
+    uint32_t w[32];                                  // the row's 32 results as bit patterns
+    if (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) {
+        const bool has_bias = p.bias_f32 != nullptr;
+        const bool relu = p.relu != 0;
+        float v[32];
+        #pragma unroll
+        for (int c = 0; c < 32; c++) v[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[c], has_bias, s_aux[c], relu);
+        if (p.absmax_out && row_ok) {
+            #pragma unroll
+            for (int c = 0; c < 32; c++)
+                if (full || (uint64_t)c < n_left) absmax_fold(absmax, v[c]);
+        }
+        if (MODE == EPI_DEQUANT_I8) {
+            if (!row_ok) return;
+            int8_t* row = static_cast<int8_t*>(p.out) + m * p.ldo + n_first;
+            uint32_t q[8];
+            #pragma unroll
+            for (int c = 0; c < 8; c++) q[c] = quantize_quad_packed(make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]), oq);
+            if (full && (((uintptr_t)row & 15) == 0)) {
+                __stcs(reinterpret_cast<uint4*>(row), make_uint4(q[0], q[1], q[2], q[3]));
+                __stcs(reinterpret_cast<uint4*>(row + 16), make_uint4(q[4], q[5], q[6], q[7]));
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 32; c++)
+                    if ((uint64_t)c < n_left) row[c] = (int8_t)((q[c >> 2] >> (8 * (c & 3))) & 0xff);
+            }
+            return;
+        }
+        #pragma unroll
+        for (int c = 0; c < 32; c++) w[c] = __float_as_uint(v[c]);
+    } else {
+        #pragma unroll
+        for (int c = 0; c < 32; c++) {
+            int32_t s = (int32_t)r[c];
+            if (MODE == EPI_RAW_I32) {
+                if (p.bias_i8 && (uint64_t)c < n_left) s = (int32_t)((uint32_t)s + (uint32_t)(int32_t)__ldg(p.bias_i8 + n_first + c));
+            } else {
+                if (p.a_row_sums) s = apply_zero_points(s, row_sum, __float_as_int(s_aux[c]), p.za, p.zb, (uint32_t)p.K);
+                s = requant_i32(s, p.sa, p.sb, p.sc);
+            }
+            w[c] = (uint32_t)s;
+        }
+    }
+    if (tma_out) {
+        if (lane == 0) bulk_wait_read_all();         // the previous chunk has left the tile
+        __syncwarp();
+        stage_row_swizzled(tile, lane, w);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_out, tile, (int32_t)n_first, (int32_t)m_base);
+            bulk_commit();
+        }
+    } else {
+        if (row_ok) {
+            uint32_t* row = static_cast<uint32_t*>(p.out) + m * p.ldo + n_first;
+            if (full && (((uintptr_t)row & 15) == 0)) {
+                #pragma unroll
+                for (int c = 0; c < 32; c += 4) __stcs(reinterpret_cast<uint4*>(row + c), make_uint4(w[c], w[c + 1], w[c + 2], w[c + 3]));
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 32; c++)
+                    if ((uint64_t)c < n_left) row[c] = w[c];
+            }
+        }
+        if (PEERS) {
+            __syncwarp();                            // the previous chunk has been read out of the tile
+            stage_row_swizzled(tile, lane, w);
+            __syncwarp();
+        }
+    }
+    if (PEERS) store_tile_to_peers(p, tile, m_base, n_first, lane);
 }
 
 // Per-tile staging of the per-column epilogue inputs into this warp's shared-memory slots.
@@ -342,12 +420,16 @@ __device__ __forceinline__ void stage_columns(const GemmProblem& p, uint64_t n0,
 template <int MODE, bool PEERS = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                  const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+                  const __grid_constant__ CUtensorMap map_out, const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n,
+                  uint32_t num_kb, int tma_out, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)kStages * STAGE_BYTES);
+    uint8_t* epi_tiles = smem + (size_t)kStages * STAGE_BYTES;
+    TcShared* sh = reinterpret_cast<TcShared*>(epi_tiles + EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = tiles_m * tiles_n;
+    // Walk the m-tiles starting at the first block of A that is in place at launch.
+    const uint32_t rotate = p.a_ready ? p.a_local_first : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
@@ -371,7 +453,11 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 uint32_t tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn, GROUP_M);
+                tile_coords(tile, tiles_m, tiles_n, tm, tn, GROUP_M, rotate);
+                if (p.a_ready && !(tm - p.a_local_first < p.a_local_count)) {
+                    // These rows come from another GPU: wait until they have landed.
+                    if (!wait_rows_ready(p.a_ready + tm, p.a_epoch, &sh->abort_flag, status)) break;
+                }
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, &sh->abort_flag, status, TC_WAIT_EMPTY)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)stage * STAGE_BYTES;
@@ -436,6 +522,8 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int ew = warp - kEpilogueWarp0;
         float* s_scales = sh->w_scales + ew * TILE_N;
         float* s_bias = sh->bias + ew * TILE_N;
+        uint8_t* my_tile = epi_tiles + ew * EPI_TILE_BYTES;
+        const bool tma = tma_out != 0;
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
@@ -443,9 +531,10 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t acc = 0, acc_phase = 0;
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn, GROUP_M);
+            tile_coords(tile, tiles_m, tiles_n, tm, tn, GROUP_M, rotate);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
-            const uint64_t m = (uint64_t)tm * TILE_M + quarter * 32 + lane;
+            const uint64_t m_base = (uint64_t)tm * TILE_M + quarter * 32;
+            const uint64_t m = m_base + lane;
             if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
@@ -459,23 +548,15 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
                 tc_wait_ld();
-                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
-                if (PEERS && MODE == EPI_DEQUANT_F32) {
-                    // The same values again (recomputed: the local store keeps no copy), for the peers.
-                    float v[32];
-                    #pragma unroll
-                    for (int c = 0; c < 32; c++)
-                        v[c] = dequant_f32((int32_t)r[c], a_scale, s_scales[chunk * 32 + c], p.bias_f32 != nullptr,
-                                           s_bias[chunk * 32 + c], p.relu != 0);
-                    float* tile = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + sizeof(TcShared)) + ew * 32 * PEER_PITCH;
-                    store_chunk_to_peers(p, v, m - (uint64_t)lane, n_first, tile, lane);
-                }
+                epilogue_chunk<MODE, PEERS>(p, &map_out, tma, my_tile, r, m_base, lane, n_first, a_scale,
+                                            s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
             if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
         }
+        if (tma && lane == 0) bulk_wait_all();           // the last stores have left shared memory and are complete
         if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
     }
 
@@ -523,7 +604,7 @@ struct __align__(16) PairShared {
     float w_scales[4 * TILE_N];
     float bias[4 * TILE_N];
 };
-constexpr size_t PAIR_SMEM_BYTES = 1024 + (size_t)kPairStages * PAIR_STAGE_BYTES + sizeof(PairShared);
+constexpr size_t PAIR_SMEM_BYTES = 1024 + (size_t)kPairStages * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + sizeof(PairShared);
 
 constexpr uint32_t kIdescI8Pair = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(PAIR_TILE_M >> 4) << 24);
 
@@ -567,10 +648,12 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                       const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+                       const __grid_constant__ CUtensorMap map_out, const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n,
+                       uint32_t num_kb, int tma_out, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    PairShared* sh = reinterpret_cast<PairShared*>(smem + (size_t)kPairStages * PAIR_STAGE_BYTES);
+    uint8_t* epi_tiles = smem + (size_t)kPairStages * PAIR_STAGE_BYTES;
+    PairShared* sh = reinterpret_cast<PairShared*>(epi_tiles + EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_cta_rank();             // 0 = leader
     const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -650,6 +733,8 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int ew = warp - kEpilogueWarp0;
         float* s_scales = sh->w_scales + ew * TILE_N;
         float* s_bias = sh->bias + ew * TILE_N;
+        uint8_t* my_tile = epi_tiles + ew * EPI_TILE_BYTES;
+        const bool tma = tma_out != 0;
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
@@ -659,7 +744,8 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn, PAIR_GROUP_M);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
-            const uint64_t m = (uint64_t)tm * PAIR_TILE_M + cta * 128 + quarter * 32 + lane;
+            const uint64_t m_base = (uint64_t)tm * PAIR_TILE_M + cta * 128 + quarter * 32;
+            const uint64_t m = m_base + lane;
             if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
             bool ok = mbar_wait_bounded(&sh->acc_full[acc], acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
@@ -673,13 +759,15 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 uint32_t r[32];
                 tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * TILE_N + (uint32_t)chunk * 32u, r);
                 tc_wait_ld();
-                store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
+                epilogue_chunk<MODE, false>(p, &map_out, tma, my_tile, r, m_base, lane, n_first, a_scale,
+                                            s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->acc_empty[acc]), 0));
             if (++acc == kAccBuffers) { acc = 0; acc_phase ^= 1; }
         }
+        if (tma && lane == 0) bulk_wait_all();
         if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
     }
 
@@ -722,15 +810,17 @@ struct __align__(16) WideShared {
     float w_scales[4 * TILE_N];
     float bias[4 * TILE_N];
 };
-constexpr size_t WIDE_SMEM_BYTES = 1024 + (size_t)kWideStages * WIDE_STAGE_BYTES + sizeof(WideShared);
+constexpr size_t WIDE_SMEM_BYTES = 1024 + (size_t)kWideStages * WIDE_STAGE_BYTES + EPI_STAGE_BYTES + sizeof(WideShared);
 
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                       const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n, uint32_t num_kb, int* status) {
+                       const __grid_constant__ CUtensorMap map_out, const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n,
+                       uint32_t num_kb, int tma_out, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    WideShared* sh = reinterpret_cast<WideShared*>(smem + (size_t)kWideStages * WIDE_STAGE_BYTES);
+    uint8_t* epi_tiles = smem + (size_t)kWideStages * WIDE_STAGE_BYTES;
+    WideShared* sh = reinterpret_cast<WideShared*>(epi_tiles + EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
 
@@ -807,6 +897,8 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const int ew = warp - kEpilogueWarp0;
         float* s_scales = sh->w_scales + ew * TILE_N;
         float* s_bias = sh->bias + ew * TILE_N;
+        uint8_t* my_tile = epi_tiles + ew * EPI_TILE_BYTES;
+        const bool tma = tma_out != 0;
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
         const QuantConsts oq = make_quant_consts(MODE == EPI_DEQUANT_I8 ? __ldg(p.out_scale) : 1.0f, p.out_zp);
         float absmax = 0.0f;
@@ -823,7 +915,8 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tc_fence_after();
             #pragma unroll 1
             for (int half = 0; half < 2; half++) {
-                const uint64_t m = (uint64_t)tm * WIDE_TILE_M + half * 128 + quarter * 32 + lane;
+                const uint64_t m_base = (uint64_t)tm * WIDE_TILE_M + half * 128 + quarter * 32;
+                const uint64_t m = m_base + lane;
                 const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
                 #pragma unroll 1
                 for (int chunk = 0; chunk < TILE_N / 32; chunk++) {
@@ -832,7 +925,8 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     uint32_t r[32];
                     tc_ld_32x32(tmem_base + ((quarter * 32u) << 16) + (uint32_t)half * TILE_N + (uint32_t)chunk * 32u, r);
                     tc_wait_ld();
-                    store_chunk<MODE>(p, r, m, n_first, a_scale, s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
+                    epilogue_chunk<MODE, false>(p, &map_out, tma, my_tile, r, m_base, lane, n_first, a_scale,
+                                                s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
                 }
             }
             tc_fence_before();
@@ -840,6 +934,7 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (lane == 0) mbar_arrive(&sh->acc_empty);
             acc_phase ^= 1;
         }
+        if (tma && lane == 0) bulk_wait_all();
         if ((MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) && p.absmax_out) absmax_publish(p.absmax_out, absmax);
     }
 
@@ -898,33 +993,82 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Map of a row-major [rows, K] int8 matrix, box = box_rows x 128 bytes, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const int8_t* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+// Tensor maps depend only on the address, the shape and the box, not on the
+// contents, so a layer that is called again with the same buffers gets its maps
+// from a small per-thread cache instead of from the driver.
+struct MapKey {
+    const void* base;
+    uint64_t dim0, dim1, stride;
+    uint32_t box0, box1;
+    int elem;                        // 1 = int8 operand, 4 = four-byte output
+    bool operator==(const MapKey& o) const {
+        return base == o.base && dim0 == o.dim0 && dim1 == o.dim1 && stride == o.stride && box0 == o.box0 &&
+               box1 == o.box1 && elem == o.elem;
+    }
+};
+constexpr int kMapCacheEntries = 16;
+struct MapCache {
+    MapKey key[kMapCacheEntries];
+    CUtensorMap map[kMapCacheEntries];
+    int used = 0, next = 0;
+};
+static thread_local MapCache t_maps;
+
+// 2-D map of a row-major matrix: dim0 contiguous elements per row, dim1 rows, row
+// stride in bytes; box0 x box1 elements per copy, 128-byte swizzle.
+static int make_map_2d(CUtensorMap* map, const void* base, int elem, uint64_t dim0, uint64_t dim1, uint64_t stride_bytes,
+                       uint32_t box0, uint32_t box1, const char* what) {
+    const MapKey key = {base, dim0, dim1, stride_bytes, box0, box1, elem};
+    for (int i = 0; i < t_maps.used; i++)
+        if (t_maps.key[i] == key) { *map = t_maps.map[i]; return 0; }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(RPLB_E_NO_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K};
-    cuuint32_t box[2] = {(cuuint32_t)TILE_K, box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(RPLB_E_BAD_ARG, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    cuuint64_t dims[2] = {(cuuint64_t)dim0, (cuuint64_t)dim1};
+    cuuint64_t strides[1] = {(cuuint64_t)stride_bytes};
+    cuuint32_t box[2] = {box0, box1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base),
+                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RPLB_E_BAD_ARG, "cuTensorMapEncodeTiled (%s) failed with CUresult %d", what, (int)r);
+    const int slot = t_maps.next;
+    t_maps.key[slot] = key;
+    t_maps.map[slot] = *map;
+    t_maps.next = (slot + 1) % kMapCacheEntries;
+    if (t_maps.used < kMapCacheEntries) t_maps.used++;
     return 0;
+}
+
+// Map of a row-major [rows, K] int8 matrix, box = box_rows x 128 bytes.
+static int make_map(CUtensorMap* map, const int8_t* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    return make_map_2d(map, base, 1, K, rows, K, (uint32_t)TILE_K, box_rows, "operand [rows,K]");
 }
 
 // Map of gemm_int8's row-major B [K, N]: inner dimension N, box = 128 N-bytes x 128 K-rows.
 static int make_map_kn(CUtensorMap* map, const int8_t* base, uint64_t K, uint64_t N) {
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return fail(RPLB_E_NO_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};
-    cuuint64_t strides[1] = {(cuuint64_t)N};
-    cuuint32_t box[2] = {128, (cuuint32_t)TILE_K};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(RPLB_E_BAD_ARG, "cuTensorMapEncodeTiled (B[K,N]) failed with CUresult %d", (int)r);
+    return make_map_2d(map, base, 1, N, K, N, 128, (uint32_t)TILE_K, "B [K,N]");
+}
+
+// Which store path this host thread's GEMMs use: 0 = through the tensor map when
+// the output allows it, 1 = always from registers.
+static thread_local int t_epilogue = 0;
+int thread_gemm_epilogue(int which) {
+    const int prev = t_epilogue;
+    if (which == 0 || which == 1) t_epilogue = which;
+    return prev;
+}
+
+// Map of the four-byte output [M, ldo] (N valid columns), box = 32 x 32 values, for
+// the epilogue's stores.  *usable = 0 when the output cannot be described (base or
+// row stride not a multiple of 16 bytes, int8 output) or the caller asked for
+// register stores; the kernel then stores from registers.
+static int make_map_out(CUtensorMap* map, const GemmProblem& p, int* usable) {
+    *usable = 0;
+    memset(map, 0, sizeof(*map));
+    if (t_epilogue == 1 || p.mode == EPI_DEQUANT_I8) return 0;
+    if (((uintptr_t)p.out & 15) || (p.ldo % 4) != 0 || p.ldo * 4 >= (1ull << 40)) return 0;
+    if (int rc = make_map_2d(map, p.out, 4, p.N, p.M, p.ldo * 4, 32, 32, "output")) return rc;
+    *usable = 1;
     return 0;
 }
 
@@ -941,22 +1085,32 @@ bool gemm_tcgen05_supports(const GemmProblem& p) {
     return tiles < 0x7fffffffull;
 }
 
-// Status word the kernel writes when a bounded wait expires: page-locked host
-// memory mapped into the device, so the host can read it without touching the
-// stream.  One word per process.
-static int* kernel_status_word() {
-    static int* word = nullptr;
+// Status words the kernels write when a bounded wait expires: page-locked host
+// memory mapped into the device, so the host can read them without touching a
+// stream.  Every host thread launches with a word of its own (threads beyond
+// kStatusSlots share), so a give-up is reported to the thread whose kernel it was.
+constexpr int kStatusSlots = 1024;
+static int* kernel_status_words() {
+    static int* words = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
         void* p = nullptr;
-        if (cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
-            word = static_cast<int*>(p);
-            *word = 0;
+        if (cudaHostAlloc(&p, kStatusSlots * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+            words = static_cast<int*>(p);
+            memset(words, 0, kStatusSlots * sizeof(int));
         } else {
             cudaGetLastError();
         }
     });
-    return word;
+    return words;
+}
+static int* kernel_status_word() {
+    static std::atomic<unsigned int> next_slot{0};
+    static thread_local int slot = -1;
+    int* words = kernel_status_words();
+    if (!words) return nullptr;
+    if (slot < 0) slot = (int)(next_slot.fetch_add(1) % kStatusSlots);
+    return words + slot;
 }
 
 // Runs the kernel above and checks that the give-up path works end to end:
@@ -987,6 +1141,21 @@ int bounded_wait_selftest(cudaStream_t st) {
     return 0;
 }
 
+// The same give-up, left in the calling thread's status word for the caller to find.
+int bounded_wait_leave_status(cudaStream_t st) {
+    int* status_host = kernel_status_word();
+    if (!status_host) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
+    int* status_dev = nullptr;
+    if (int rc = cuda_ok(cudaHostGetDevicePointer((void**)&status_dev, status_host, 0), "cudaHostGetDevicePointer")) return rc;
+    int* result = nullptr;
+    if (int rc = cuda_ok(cudaMalloc((void**)&result, 2 * sizeof(int)), "cudaMalloc(selftest)")) return rc;
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(status_dev, result, 2000000LL);
+    int rc = launched("bounded_wait_selftest_kernel");
+    if (!rc) rc = cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize(selftest)");
+    cudaFree(result);
+    return rc;
+}
+
 int gemm_tcgen05_status(bool clear) {
     int* w = kernel_status_word();
     if (!w) return 0;
@@ -995,22 +1164,45 @@ int gemm_tcgen05_status(bool clear) {
     return v;
 }
 
+// Opting in to more than 48 KiB of dynamic shared memory is a per-device
+// attribute of each kernel: set once per (kernel, device), remembered here.
+constexpr int kMaxDevices = 64;
+enum KernelFamily : int { FAM_TC = 0, FAM_TC_PEERS = 1, FAM_PAIR = 2, FAM_WIDE = 3, FAM_COUNT = 4 };
+static std::atomic<uint64_t> g_attr_done[FAM_COUNT][4];      // one bit per device ordinal
+static std::atomic<int> g_resident_pairs[kMaxDevices][4];    // 0 = not asked yet
+
+template <typename Kernel>
+static int ensure_smem_attr(Kernel kernel, int family, int mode, size_t bytes, const char* what) {
+    int dev = 0;
+    if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    if (tracked && ((g_attr_done[family][mode].load(std::memory_order_acquire) >> dev) & 1ull)) return 0;
+    if (int rc = cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what)) return rc;
+    if (tracked) g_attr_done[family][mode].fetch_or(1ull << dev, std::memory_order_release);
+    return 0;
+}
+
 template <int MODE, bool PEERS = false>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t tiles_m,
-                     uint32_t tiles_n, uint32_t num_kb, int* status_dev, unsigned int grid, cudaStream_t st) {
-    // Opt in to more than 48 KiB of dynamic shared memory.  The attribute is
-    // per device, so it is set on every launch (a cheap host-side call).
-    const size_t smem = TC_SMEM_BYTES + (PEERS ? PEER_STAGE_BYTES : 0);      // the peers' staging tiles follow TcShared
-    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_kernel<MODE, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)smem), "cudaFuncSetAttribute(gemm_i8_tc_kernel)")) return rc;
-    gemm_i8_tc_kernel<MODE, PEERS><<<grid, TC_THREADS, smem, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmProblem& p, uint32_t tiles_m,
+                     uint32_t tiles_n, uint32_t num_kb, int tma_out, int* status_dev, unsigned int grid, cudaStream_t st) {
+    if (int rc = ensure_smem_attr(gemm_i8_tc_kernel<MODE, PEERS>, PEERS ? FAM_TC_PEERS : FAM_TC, MODE, TC_SMEM_BYTES,
+                                  "cudaFuncSetAttribute(gemm_i8_tc_kernel)")) return rc;
+    gemm_i8_tc_kernel<MODE, PEERS><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev);
     return launched("gemm_i8_tc_kernel");
 }
 
 // How many CTA pairs can be resident at once (SMs pair up inside a TPC; a GPC
-// with an odd number of usable SMs leaves one without a partner).
+// with an odd number of usable SMs leaves one without a partner).  Asked once
+// per device and epilogue mode.
 template <int MODE>
 static int max_resident_pairs(int* pairs) {
+    int dev = 0;
+    if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    if (tracked) {
+        const int known = g_resident_pairs[dev][MODE].load(std::memory_order_acquire);
+        if (known > 0) { *pairs = known; return 0; }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74);
     cfg.blockDim = dim3(TC_THREADS);
@@ -1024,15 +1216,16 @@ static int max_resident_pairs(int* pairs) {
     cfg.numAttrs = 1;
     int n = 0;
     if (int rc = cuda_ok(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc_pair_kernel<MODE>, &cfg), "cudaOccupancyMaxActiveClusters")) return rc;
+    if (tracked && n > 0) g_resident_pairs[dev][MODE].store(n, std::memory_order_release);
     *pairs = n;
     return 0;
 }
 
 template <int MODE>
-static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t num_kb,
-                          int* status_dev, cudaStream_t st) {
-    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)PAIR_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_pair_kernel)")) return rc;
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmProblem& p, uint32_t num_kb,
+                          int tma_out, int* status_dev, cudaStream_t st) {
+    if (int rc = ensure_smem_attr(gemm_i8_tc_pair_kernel<MODE>, FAM_PAIR, MODE, PAIR_SMEM_BYTES,
+                                  "cudaFuncSetAttribute(gemm_i8_tc_pair_kernel)")) return rc;
     int pairs = 0;
     if (int rc = max_resident_pairs<MODE>(&pairs)) return rc;
     if (pairs <= 0) return fail(RPLB_E_UNSUPPORTED, "no CTA pair fits on this device");
@@ -1052,21 +1245,21 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, const Ge
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_tc_pair_kernel<MODE>, ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_tc_pair_kernel<MODE>, ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev);
     if (e != cudaSuccess) return cuda_ok(e, "cudaLaunchKernelEx(gemm_i8_tc_pair_kernel)");
     return launched("gemm_i8_tc_pair_kernel");
 }
 
 template <int MODE>
-static int launch_tc_wide(const CUtensorMap& ma, const CUtensorMap& mw, const GemmProblem& p, uint32_t num_kb,
-                          int* status_dev, unsigned int sms, cudaStream_t st) {
-    if (int rc = cuda_ok(cudaFuncSetAttribute(gemm_i8_tc_wide_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)WIDE_SMEM_BYTES), "cudaFuncSetAttribute(gemm_i8_tc_wide_kernel)")) return rc;
+static int launch_tc_wide(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, const GemmProblem& p, uint32_t num_kb,
+                          int tma_out, int* status_dev, unsigned int sms, cudaStream_t st) {
+    if (int rc = ensure_smem_attr(gemm_i8_tc_wide_kernel<MODE>, FAM_WIDE, MODE, WIDE_SMEM_BYTES,
+                                  "cudaFuncSetAttribute(gemm_i8_tc_wide_kernel)")) return rc;
     const uint32_t tiles_m = (uint32_t)((p.M + WIDE_TILE_M - 1) / WIDE_TILE_M);
     const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
     const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
     const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
-    gemm_i8_tc_wide_kernel<MODE><<<grid, TC_THREADS, WIDE_SMEM_BYTES, st>>>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev);
+    gemm_i8_tc_wide_kernel<MODE><<<grid, TC_THREADS, WIDE_SMEM_BYTES, st>>>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev);
     return launched("gemm_i8_tc_wide_kernel");
 }
 
@@ -1076,7 +1269,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "tcgen05 GEMM needs W as [N,K], K %% 16 == 0, 16-byte aligned A and W");
     if (int prev = gemm_tcgen05_status(true))
-        return fail(RPLB_E_KERNEL, "an earlier tcgen05 GEMM gave up waiting (code %d)", prev);
+        return fail(RPLB_E_KERNEL, "an earlier tcgen05 GEMM of this thread gave up waiting (code %d)", prev);
     int* status_host = kernel_status_word();
     if (!status_host) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
     int* status_dev = nullptr;
@@ -1092,6 +1285,14 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
             return fail(RPLB_E_UNSUPPORTED, "peer destinations need the fp32 epilogue, W as [N,K] and at most %d peers", kMaxPeers);
         variant = 1;
     }
+    if (p.a_ready) {
+        // Only the 128 x 256 kernel waits for rows that are still arriving.
+        const uint64_t tiles_m = (p.M + TILE_M - 1) / TILE_M;
+        if (p.b_is_kn || (uint64_t)p.a_local_first + p.a_local_count > tiles_m || (p.a_local_first >= tiles_m && tiles_m))
+            return fail(RPLB_E_BAD_ARG, "arriving rows: local blocks [%u, +%u) outside the %llu row blocks of A",
+                        p.a_local_first, p.a_local_count, (unsigned long long)tiles_m);
+        variant = 1;
+    }
     if (variant == 0) {
         // Measured on B200 (1000 W cap): un-throttled, the pair kernel keeps the
         // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster;
@@ -1103,15 +1304,17 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         const double macs = (double)p.M * (double)p.N * (double)p.K;
         variant = (pair_tiles >= sms / 2 && macs < 1.1e12) ? 2 : 1;
     }
-    CUtensorMap ma, mw;
+    CUtensorMap ma, mw, mo;
+    int tma_out = 0;
+    if (int rc = make_map_out(&mo, p, &tma_out)) return rc;
     if (variant == 3) {
         if (int rc = make_map(&ma, p.A, p.M, p.K, WIDE_TILE_M)) return rc;
         if (int rc = make_map(&mw, p.B, p.N, p.K, TILE_N)) return rc;
         switch (p.mode) {
-            case EPI_RAW_I32:     return launch_tc_wide<EPI_RAW_I32>(ma, mw, p, num_kb, status_dev, sms, st);
-            case EPI_REQUANT_I32: return launch_tc_wide<EPI_REQUANT_I32>(ma, mw, p, num_kb, status_dev, sms, st);
-            case EPI_DEQUANT_F32: return launch_tc_wide<EPI_DEQUANT_F32>(ma, mw, p, num_kb, status_dev, sms, st);
-            case EPI_DEQUANT_I8:  return launch_tc_wide<EPI_DEQUANT_I8>(ma, mw, p, num_kb, status_dev, sms, st);
+            case EPI_RAW_I32:     return launch_tc_wide<EPI_RAW_I32>(ma, mw, mo, p, num_kb, tma_out, status_dev, sms, st);
+            case EPI_REQUANT_I32: return launch_tc_wide<EPI_REQUANT_I32>(ma, mw, mo, p, num_kb, tma_out, status_dev, sms, st);
+            case EPI_DEQUANT_F32: return launch_tc_wide<EPI_DEQUANT_F32>(ma, mw, mo, p, num_kb, tma_out, status_dev, sms, st);
+            case EPI_DEQUANT_I8:  return launch_tc_wide<EPI_DEQUANT_I8>(ma, mw, mo, p, num_kb, tma_out, status_dev, sms, st);
         }
         return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
     }
@@ -1119,10 +1322,10 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         if (int rc = make_map(&ma, p.A, p.M, p.K, 128)) return rc;
         if (int rc = make_map(&mw, p.B, p.N, p.K, 128)) return rc;
         switch (p.mode) {
-            case EPI_RAW_I32:     return launch_tc_pair<EPI_RAW_I32>(ma, mw, p, num_kb, status_dev, st);
-            case EPI_REQUANT_I32: return launch_tc_pair<EPI_REQUANT_I32>(ma, mw, p, num_kb, status_dev, st);
-            case EPI_DEQUANT_F32: return launch_tc_pair<EPI_DEQUANT_F32>(ma, mw, p, num_kb, status_dev, st);
-            case EPI_DEQUANT_I8:  return launch_tc_pair<EPI_DEQUANT_I8>(ma, mw, p, num_kb, status_dev, st);
+            case EPI_RAW_I32:     return launch_tc_pair<EPI_RAW_I32>(ma, mw, mo, p, num_kb, tma_out, status_dev, st);
+            case EPI_REQUANT_I32: return launch_tc_pair<EPI_REQUANT_I32>(ma, mw, mo, p, num_kb, tma_out, status_dev, st);
+            case EPI_DEQUANT_F32: return launch_tc_pair<EPI_DEQUANT_F32>(ma, mw, mo, p, num_kb, tma_out, status_dev, st);
+            case EPI_DEQUANT_I8:  return launch_tc_pair<EPI_DEQUANT_I8>(ma, mw, mo, p, num_kb, tma_out, status_dev, st);
         }
         return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
     }
@@ -1133,12 +1336,12 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
     const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
     switch (p.mode) {
-        case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
-        case EPI_REQUANT_I32: return launch_tc<EPI_REQUANT_I32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+        case EPI_RAW_I32:     return launch_tc<EPI_RAW_I32>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev, grid, st);
+        case EPI_REQUANT_I32: return launch_tc<EPI_REQUANT_I32>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev, grid, st);
         case EPI_DEQUANT_F32:
-            if (p.n_peers > 0) return launch_tc<EPI_DEQUANT_F32, true>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
-            return launch_tc<EPI_DEQUANT_F32>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
-        case EPI_DEQUANT_I8:  return launch_tc<EPI_DEQUANT_I8>(ma, mw, p, tiles_m, tiles_n, num_kb, status_dev, grid, st);
+            if (p.n_peers > 0) return launch_tc<EPI_DEQUANT_F32, true>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev, grid, st);
+            return launch_tc<EPI_DEQUANT_F32>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev, grid, st);
+        case EPI_DEQUANT_I8:  return launch_tc<EPI_DEQUANT_I8>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev, grid, st);
     }
     return fail(RPLB_E_BAD_ARG, "unknown epilogue mode %d", p.mode);
 }

@@ -127,6 +127,18 @@ minmax_kernel(const float* __restrict__ x, uint64_t n, uint64_t head, uint64_t n
     }
 }
 
+// A tensor whose rows are spread over several GPUs: each reduces its rows, the
+// pairs (-min, max) are combined with one max-reduction across the GPUs, and
+// the parameters are then derived from the combined pair by the very statements
+// the single-GPU reduction ends with (IEEE division included).
+__global__ void qparams_to_pair_kernel(const rplb_qparams* __restrict__ params, float* __restrict__ pair) {
+    pair[0] = -params->true_min;
+    pair[1] = params->true_max;
+}
+__global__ void qparams_from_pair_kernel(const float* __restrict__ pair, rplb_qparams* __restrict__ params) {
+    finalize_params(-pair[0], pair[1], params->first, params);
+}
+
 // ---------------------------------------------------------------------------
 // quantize  (src/rpl_core.c:521-527)
 // ---------------------------------------------------------------------------
@@ -461,6 +473,18 @@ int rplb_minmax_f32(const float* x, uint64_t n, rplb_qparams* params, void* stre
     return launch_minmax(x, n, params, as_stream(stream));
 }
 
+int rplb_qparams_to_pair(const rplb_qparams* params, float* pair, void* stream) {
+    if (!params || !pair) return fail(RPLB_E_BAD_ARG, "rplb_qparams_to_pair: null pointer");
+    qparams_to_pair_kernel<<<1, 1, 0, as_stream(stream)>>>(params, pair);
+    return launched("qparams_to_pair_kernel");
+}
+
+int rplb_qparams_from_pair(const float* pair, rplb_qparams* params, void* stream) {
+    if (!params || !pair) return fail(RPLB_E_BAD_ARG, "rplb_qparams_from_pair: null pointer");
+    qparams_from_pair_kernel<<<1, 1, 0, as_stream(stream)>>>(pair, params);
+    return launched("qparams_from_pair_kernel");
+}
+
 int rplb_quantize_f32_i8(const float* x, int8_t* q, uint64_t n, float scale, int32_t zero_point, void* stream) {
     return launch_quantize(x, q, n, scale, zero_point, nullptr, nullptr, false, as_stream(stream));
 }
@@ -584,7 +608,9 @@ static __device__ __align__(256) StaticMinmaxScratch g_static_minmax;
 
 // Device address of the array above, per device ordinal.  In host code the
 // symbol's name is only a handle: the address a kernel can use has to be asked
-// for, with the device in question current.
+// for, with the device in question current.  The answer is kept for the life of
+// the process: a cudaDeviceReset() unloads the library's device image, after
+// which the library as a whole (not only this cache) must not be used.
 constexpr int kMaxDevices = 64;
 static StaticMinmaxScratch* g_static_minmax_addr[kMaxDevices];
 static std::mutex g_static_minmax_mu;

@@ -629,6 +629,52 @@ void quantized_model_free(QuantizedModel* qm) {
     free(qm);
 }
 
+/* The per-channel counterpart of model_quantize: what the reference's flag
+ * announces and leaves undone (src/rpl_quantization.c:286-292).  Parameters with
+ * two or more dimensions (weights [out, ...]) are quantized per output channel,
+ * i.e. per row of shape[0] (tensor_quantize_per_channel, axis 0); the others
+ * (biases) get one scale for the whole tensor, stored as a single channel, which
+ * is tensor_quantize_int8_symmetric's arithmetic (src/rpl_quantization.c:79-90
+ * and :136-154 are the same statements over one block). */
+PerChannelQuantizedModel* model_quantize_per_channel(Tensor** parameters, uint32_t num_params) {
+    if (!parameters && num_params) return NULL;
+    PerChannelQuantizedModel* qm = (PerChannelQuantizedModel*)calloc(1, sizeof(PerChannelQuantizedModel));
+    if (!qm) return NULL;
+    qm->num_params = num_params;
+    qm->fp32_params = parameters;
+    qm->int8_params = (PerChannelQuantizedTensor**)calloc(num_params ? num_params : 1, sizeof(PerChannelQuantizedTensor*));
+    if (!qm->int8_params) { free(qm); return NULL; }
+    for (uint32_t i = 0; i < num_params; i++) {
+        const Tensor* t = parameters[i];
+        if (!t) continue;
+        if (t->dims >= 2) {
+            qm->int8_params[i] = tensor_quantize_per_channel(t, 0);
+        } else {
+            Tensor view = *t;                      /* the same elements seen as one row */
+            view.dims = 2;
+            view.shape[0] = 1;
+            view.shape[1] = t->size;
+            PerChannelQuantizedTensor* q = tensor_quantize_per_channel(&view, 0);
+            if (q) {
+                q->dims = t->dims;
+                memset(q->shape, 0, sizeof(q->shape));
+                memcpy(q->shape, t->shape, t->dims * sizeof(uint32_t));
+            }
+            qm->int8_params[i] = q;
+        }
+        if (!qm->int8_params[i]) { per_channel_quantized_model_free(qm); return NULL; }
+    }
+    qm->is_quantized = true;
+    return qm;
+}
+
+void per_channel_quantized_model_free(PerChannelQuantizedModel* qm) {
+    if (!qm) return;
+    for (uint32_t i = 0; i < qm->num_params; i++) per_channel_quantized_tensor_free(qm->int8_params[i]);
+    free(qm->int8_params);
+    free(qm);
+}
+
 /* ------------------------------------------------------------------------
  * Quantized weights on disk.
  *
@@ -697,10 +743,20 @@ PerChannelQuantizedTensor** quantized_weights_load(const char* path, uint32_t* n
         ok = t && fread(&t->dims, 4, 1, f) == 1 && t->dims <= MAX_DIMS &&
              fread(t->shape, 4, t->dims, f) == t->dims && fread(&size, 4, 1, f) == 1;
         if (!ok) break;
+        /* The element count must be the product of the shape (a file written by quantized_weights_save always is). */
+        uint64_t prod = 1;
+        for (uint32_t d = 0; d < t->dims; d++) prod *= t->shape[d];
+        ok = prod == size;
+        if (!ok) break;
         /* The tensor owns its blocks from the moment they exist, so the error path below frees them. */
         t->data = (int8_t*)rpitorch_aligned_alloc(64, size ? size : 1);
         ok = t->data && fread(t->data, 1, size, f) == size && fread(&t->num_channels, 4, 1, f) == 1 &&
              t->num_channels <= size + 1u;
+        /* Channels are equal contiguous blocks: their count divides the size and is one of the
+         * tensor's extents (tensor_quantize_per_channel takes it from shape[axis]), or 1. */
+        int axis_ok = t->num_channels == 1 || (t->num_channels == 0 && size == 0);
+        for (uint32_t d = 0; d < t->dims; d++) axis_ok = axis_ok || t->num_channels == t->shape[d];
+        ok = ok && axis_ok && (t->num_channels ? size % t->num_channels == 0 : size == 0);
         if (!ok) break;
         const size_t cb = t->num_channels ? (size_t)t->num_channels * 4 : 4;
         t->scales = (float*)malloc(cb);

@@ -43,6 +43,30 @@ static std::mutex g_scratch_mu;
 static std::map<std::pair<int, cudaStream_t>, ScratchBlock> g_scratch;
 static constexpr size_t kControlBytes = 256;
 
+// Device allocator behind rplb_malloc / rplb_free and the scratch blocks:
+// cudaMalloc / cudaFree unless the application installed its own pair.
+static rplb_alloc_fn g_alloc_fn = nullptr;
+static rplb_free_fn g_free_fn = nullptr;
+
+int device_alloc(void** p, size_t bytes, const char* what) {
+    *p = nullptr;
+    if (g_alloc_fn) {
+        const int rc = g_alloc_fn(p, bytes);
+        if (rc != 0 || !*p) {
+            *p = nullptr;
+            return fail(rc != 0 ? rc : (int)cudaErrorMemoryAllocation, "%s: the installed allocator could not provide %zu bytes", what, bytes);
+        }
+        return 0;
+    }
+    return cuda_ok(cudaMalloc(p, bytes), what);
+}
+
+int device_free(void* p) {
+    if (!p) return 0;
+    if (g_free_fn) return g_free_fn(p);
+    return cuda_ok(cudaFree(p), "cudaFree");
+}
+
 int scratch_for(cudaStream_t stream, size_t bytes, Scratch* out) {
     int dev = 0;
     if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
@@ -50,15 +74,23 @@ int scratch_for(cudaStream_t stream, size_t bytes, Scratch* out) {
     ScratchBlock& b = g_scratch[std::make_pair(dev, stream)];
     size_t want = kControlBytes + ((bytes + 255) & ~size_t(255));
     if (b.bytes < want) {
+        // A block cannot be allocated, grown or cleared while the stream records a
+        // graph: the graph would keep the address of a block that a later call
+        // frees.  Reserve the largest size first (rplb_scratch_reserve), then capture.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+        if (cap != cudaStreamCaptureStatusNone)
+            return fail(RPLB_E_UNSUPPORTED, "the stream is being captured and its scratch block (%zu bytes) is too small for %zu: "
+                        "call rplb_scratch_reserve before the capture", b.bytes, want);
         if (b.base) {
             // Work queued on the stream may still use the old block.
             if (int rc = cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize")) return rc;
-            cudaFree(b.base);
+            device_free(b.base);
             b.base = nullptr;
             b.bytes = 0;
         }
         size_t grow = want < (size_t(1) << 20) ? (size_t(1) << 20) : want;
-        if (int rc = cuda_ok(cudaMalloc(&b.base, grow), "cudaMalloc(scratch)")) return rc;
+        if (int rc = device_alloc(&b.base, grow, "scratch allocation")) return rc;
         if (int rc = cuda_ok(cudaMemsetAsync(b.base, 0, kControlBytes, stream), "cudaMemsetAsync(scratch)")) return rc;
         b.bytes = grow;
     }
@@ -100,16 +132,46 @@ int rplb_device_count(void) {
 
 int rplb_device_sm_count(void) { return sm_count(); }
 
+int rplb_set_device(int ordinal) { return cuda_ok(cudaSetDevice(ordinal), "cudaSetDevice"); }
+
 uint64_t rplb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int rplb_malloc(void** dptr, size_t bytes) {
     if (!dptr) return fail(RPLB_E_BAD_ARG, "rplb_malloc: null result pointer");
     *dptr = nullptr;
     if (bytes == 0) bytes = 1;
-    return cuda_ok(cudaMalloc(dptr, bytes), "cudaMalloc");
+    return device_alloc(dptr, bytes, "cudaMalloc");
 }
 
-int rplb_free(void* dptr) { return dptr ? cuda_ok(cudaFree(dptr), "cudaFree") : 0; }
+int rplb_free(void* dptr) { return device_free(dptr); }
+
+int rplb_set_allocator(rplb_alloc_fn alloc_fn, rplb_free_fn free_fn) {
+    if ((alloc_fn == nullptr) != (free_fn == nullptr))
+        return fail(RPLB_E_BAD_ARG, "rplb_set_allocator: give both functions or neither");
+    g_alloc_fn = alloc_fn;
+    g_free_fn = free_fn;
+    return 0;
+}
+
+int rplb_scratch_reserve(void* stream, size_t bytes) {
+    Scratch sc;
+    return scratch_for(as_stream(stream), bytes, &sc);
+}
+
+int rplb_scratch_release(void* stream) {
+    int dev = 0;
+    if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    cudaStream_t st = as_stream(stream);
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    auto it = g_scratch.find(std::make_pair(dev, st));
+    if (it == g_scratch.end()) return 0;
+    if (it->second.base) {
+        if (int rc = cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return rc;
+        device_free(it->second.base);
+    }
+    g_scratch.erase(it);
+    return 0;
+}
 
 int rplb_host_alloc(void** hptr, size_t bytes) {
     if (!hptr) return fail(RPLB_E_BAD_ARG, "rplb_host_alloc: null result pointer");

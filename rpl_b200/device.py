@@ -40,6 +40,12 @@ def gemm_backend(which):
     return int(capi.load().rplb_gemm_backend(int(which)))
 
 
+def gemm_epilogue(which):
+    """0 = four-byte outputs leave through TMA tensor stores when the output allows it, 1 = always
+    stored from registers; returns the previous setting (per host thread)."""
+    return int(capi.load().rplb_gemm_epilogue(int(which)))
+
+
 def kernel_status(clear=True):
     return int(capi.load().rplb_kernel_status(1 if clear else 0))
 
@@ -51,6 +57,20 @@ def minmax(x, params=None):
     if params is None:
         params = torch.empty(8, dtype=torch.float32, device=x.device)
     capi.call("rplb_minmax_f32", _p(x), x.numel(), _p(params), _stream())
+    return params
+
+
+def qparams_to_pair(params, pair=None):
+    """(-min, max) of a device ``rplb_qparams`` as two device floats, ready for a max-reduction across ranks."""
+    if pair is None:
+        pair = torch.empty(2, dtype=torch.float32, device=params.device)
+    capi.call("rplb_qparams_to_pair", _p(params), _p(pair), _stream())
+    return pair
+
+
+def qparams_from_pair(pair, params):
+    """All parameters (scales, zero point) from a combined (-min, max) pair, as the min/max kernel derives them."""
+    capi.call("rplb_qparams_from_pair", _p(pair), _p(params), _stream())
     return params
 
 
@@ -209,6 +229,26 @@ def linear_i8_dequant_peers(x, w, a_scale, w_scales, out, peer_ptrs, bias=None, 
     ptrs = (C.c_void_p * max(1, len(peer_ptrs)))(*[int(q) for q in peer_ptrs])
     capi.call("rplb_linear_i8_dequant_f32_peers", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
               _p(bias), 1 if relu else 0, ptrs, len(peer_ptrs), _stream())
+    return out
+
+
+def linear_i8_dequant_arriving(x, w, a_scale, w_scales, ready, epoch, local_first_block, local_blocks,
+                               bias=None, relu=False, out=None):
+    """``linear_i8_dequant`` over an activation whose 128-row blocks may still be arriving from other
+    GPUs: ``ready`` is an int32/uint32 CUDA tensor with one word per block, a block is complete once its
+    word has reached ``epoch``; blocks ``[local_first_block, +local_blocks)`` are complete at launch."""
+    _need(x, torch.int8, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    M, K = x.shape
+    N = w.shape[0]
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    capi.call("rplb_linear_i8_dequant_f32_arriving", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
+              _p(bias), 1 if relu else 0, _p(ready), int(epoch) & 0xFFFFFFFF, int(local_first_block), int(local_blocks), _stream())
     return out
 
 

@@ -63,7 +63,51 @@ def global_absmax_scale(local_absmax, group=None):
     division the single-device reduction performs)."""
     t = local_absmax.clone()
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-    return t / 127.0
+    # Tensor / tensor is an IEEE division on every backend; tensor / python scalar is
+    # turned into a multiplication by the rounded reciprocal on CUDA, which differs in the last bit.
+    return t / torch.full_like(t, 127.0)
+
+
+class RankLeft(RuntimeError):
+    """Raised before a step is launched when other ranks have announced that they are gone."""
+
+    def __init__(self, ranks, step):
+        super().__init__("rank(s) %s left before step %d" % (ranks, step))
+        self.ranks, self.step = list(ranks), step
+
+
+class Membership:
+    """Who is still taking part, kept in the process group's key-value store.
+
+    A step of the sharded layer contains collectives, so a rank that has gone must be
+    noticed on the host, before the next launch: nothing may wait for it on the GPU.
+    A rank calls ``arrive(step)`` when it is ready for a step and ``leave(step)``
+    instead when it stops (only between steps, with none of its kernels or
+    collectives in flight); ``check(step)`` waits until every other rank has done one
+    or the other and raises ``RankLeft`` naming those that left.
+    """
+
+    def __init__(self, store, rank, world, timeout_s=20.0):
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world, timeout_s
+
+    def _key(self, rank, step):
+        return "rplb/member/%d/%d" % (step, rank)
+
+    def arrive(self, step):
+        self.store.set(self._key(self.rank, step), "here")
+
+    def leave(self, step):
+        self.store.set(self._key(self.rank, step), "left")
+
+    def check(self, step):
+        import datetime
+        if step == 0:
+            return
+        others = [r for r in range(self.world) if r != self.rank]
+        self.store.wait([self._key(r, step) for r in others], datetime.timedelta(seconds=self.timeout_s))
+        gone = [r for r in others if self.store.get(self._key(r, step)) == b"left"]
+        if gone:
+            raise RankLeft(gone, step)
 
 
 class ShardedQuantizedLinear:
@@ -86,6 +130,7 @@ class ShardedQuantizedLinear:
         self.relu = relu
         self._xq = None
         self._params = None
+        self._pair = None
         self._dev_in = None
         self._dev_out = None
         self._copy_stream = None
@@ -114,11 +159,7 @@ class ShardedQuantizedLinear:
         a_scale = self._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
         if self.world > 1 and self.shard_reduction and dist.is_initialized():
             r0, rc = shard_range(M, self.world, self.rank, 1)
-            local = D.minmax(x[r0:r0 + rc])
-            pair = torch.stack((-local[D.QPARAM_MIN], local[D.QPARAM_MAX]))
-            dist.all_reduce(pair, op=dist.ReduceOp.MAX, group=self.group)
-            # fmaxf(|min|, |max|) / 127.0f, the reference's statement, in fp32 on the device
-            a_scale.copy_((torch.maximum(pair[0].abs(), pair[1].abs()) / 127.0).reshape(1))
+            self._reduce_scale(x[r0:r0 + rc])
             D.quantize_dev(x, a_scale, out=self._xq)
         else:
             D.quantize_symmetric(x, out=self._xq, params=self._params)
@@ -165,13 +206,22 @@ class ShardedQuantizedLinear:
         a_scale = self._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
         if self.world > 1 and self.shard_reduction and dist.is_initialized():
             r0, rc = shard_range(M, self.world, self.rank, 1)
-            local = D.minmax(x[r0:r0 + rc])
-            pair = torch.stack((-local[D.QPARAM_MIN], local[D.QPARAM_MAX]))
-            dist.all_reduce(pair, op=dist.ReduceOp.MAX, group=self.group)
-            a_scale.copy_((torch.maximum(pair[0].abs(), pair[1].abs()) / 127.0).reshape(1))
+            self._reduce_scale(x[r0:r0 + rc])
         else:
             D.minmax(x, params=self._params)
         return a_scale
+
+    def _reduce_scale(self, rows):
+        """min/max of this rank's rows, a max-all-reduce of (-min, max), and the parameters
+        from the combined pair: all arithmetic stays in the library's kernels (the division
+        by 127 is the IEEE one of the single-GPU reduction)."""
+        from . import device as D
+        D.minmax(rows, params=self._params)
+        if self._pair is None:
+            self._pair = torch.empty(2, dtype=torch.float32, device=rows.device)
+        D.qparams_to_pair(self._params, self._pair)
+        dist.all_reduce(self._pair, op=dist.ReduceOp.MAX, group=self.group)
+        D.qparams_from_pair(self._pair, self._params)
 
     def forward_overlapped(self, x, out=None, row_chunks=4, gemm_events=None):
         """Same result as ``forward``; the quantize pass is pipelined under the GEMM.
@@ -272,8 +322,8 @@ class ShardedQuantizedLinear:
 class _RawBlock:
     """A device block that torch can view without owning it."""
 
-    def __init__(self, ptr, shape):
-        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False),
+    def __init__(self, ptr, shape, typestr="<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
                                          "version": 2, "strides": None}
 
 
@@ -392,3 +442,102 @@ class HostPipeline:
     def drain(self):
         self.s_out.synchronize()
         torch.cuda.current_stream(self.din[0].device).synchronize()
+
+
+class RowShardedLinear:
+    """Binding of ``rplb_sharded_linear_*``: the quantized Linear with output columns AND
+    activation rows split over the ranks, run entirely by ``librpl.so`` (its own NCCL
+    communicator, peer copies of the int8 rows under the GEMM).
+
+    ``torch.distributed`` is used once, to hand rank 0's NCCL id to the other ranks.
+    ``wq`` / ``w_scales`` / ``bias`` are this rank's weight rows (``columns(n_total, ...)``
+    tells which), already in device memory.
+    """
+
+    def __init__(self, wq, w_scales, bias, n_total, max_rows, rank=0, world=1, group=None):
+        import ctypes as C
+
+        from . import capi
+        self._capi, self._C = capi, C
+        self.rank, self.world, self.n_total, self.max_rows = rank, world, int(n_total), int(max_rows)
+        self.wq, self.w_scales, self.bias = wq, w_scales, bias          # keep the tensors alive
+        self.K = int(wq.shape[1])
+        ident = None
+        if world > 1:
+            raw = (C.c_char * capi.RPLB_NCCL_ID_BYTES)()
+            if rank == 0:
+                capi.call("rplb_nccl_unique_id", raw)
+            box = [bytes(raw.raw)]
+            dist.broadcast_object_list(box, src=0, group=group)
+            ident = (C.c_char * capi.RPLB_NCCL_ID_BYTES).from_buffer_copy(box[0])
+        self.handle = C.c_void_p()
+        capi.call("rplb_sharded_linear_create", C.byref(self.handle), rank, world, ident, None, self.max_rows, self.K,
+                  self.n_total, C.c_void_p(wq.data_ptr()), C.c_void_p(w_scales.data_ptr()),
+                  C.c_void_p(bias.data_ptr()) if bias is not None else None)
+        b, c = C.c_uint64(), C.c_uint64()
+        capi.call("rplb_sharded_linear_columns", self.handle, C.byref(b), C.byref(c))
+        self.col_begin, self.col_count = int(b.value), int(c.value)
+        if self.col_count != wq.shape[0]:
+            raise ValueError("this rank owns %d columns, %d weight rows were given" % (self.col_count, wq.shape[0]))
+
+    def rows(self, M):
+        """(begin, count) of this rank's rows of an ``[M, K]`` activation."""
+        b, c = self._C.c_uint64(), self._C.c_uint64()
+        self._capi.call("rplb_sharded_linear_rows", self.handle, int(M), self._C.byref(b), self._C.byref(c))
+        return int(b.value), int(c.value)
+
+    def forward(self, x_local, M, out=None, relu=False):
+        """x_local: this rank's fp32 rows ``[rows(M)[1], K]`` on the device -> fp32 column block ``[M, col_count]``."""
+        C = self._C
+        if out is None:
+            out = torch.empty((M, self.col_count), dtype=torch.float32, device=self.wq.device)
+        ldo = out.stride(0) if M > 1 else max(self.col_count, out.stride(0))
+        self._capi.call("rplb_sharded_linear_forward", self.handle, C.c_void_p(x_local.data_ptr()), int(M),
+                        C.c_void_p(out.data_ptr()), int(ldo), 1 if relu else 0,
+                        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def quantize(self, x_local, M):
+        """First half of ``forward``: scale agreement, quantization of the local rows, start of their transfer."""
+        C = self._C
+        self._capi.call("rplb_sharded_linear_quantize", self.handle, C.c_void_p(x_local.data_ptr()), int(M),
+                        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+    def gemm(self, M, out, relu=False):
+        """Second half of ``forward``: the contraction over all ``M`` rows of the activation quantized last."""
+        C = self._C
+        ldo = out.stride(0) if M > 1 else max(self.col_count, out.stride(0))
+        self._capi.call("rplb_sharded_linear_gemm", self.handle, int(M), C.c_void_p(out.data_ptr()), int(ldo),
+                        1 if relu else 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def activation(self, M):
+        """The whole int8 activation as this rank holds it after a forward, and its scale (views, not copies)."""
+        C = self._C
+        q, s = C.c_void_p(), C.c_void_p()
+        self._capi.call("rplb_sharded_linear_activation", self.handle, C.byref(q), C.byref(s))
+        dev = self.wq.device
+        xq = torch.as_tensor(_RawBlock(q.value, (M, self.K), "|i1"), device=dev)
+        scale = torch.as_tensor(_RawBlock(s.value, (1,)), device=dev)
+        return xq, scale
+
+    def gather(self, block, M):
+        C = self._C
+        full = torch.empty((M, self.n_total), dtype=torch.float32, device=block.device)
+        self._capi.call("rplb_sharded_linear_gather", self.handle, C.c_void_p(block.data_ptr()), int(block.stride(0)), int(M),
+                        C.c_void_p(full.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        return full
+
+    def submit_host(self, x_local_host, M, out_host, relu=False, row_blocks=0, stream=None):
+        C = self._C
+        self._capi.call("rplb_sharded_linear_submit_host", self.handle, C.c_void_p(x_local_host.data_ptr()), int(M),
+                        C.c_void_p(out_host.data_ptr()), 1 if relu else 0, int(row_blocks),
+                        C.c_void_p(stream.cuda_stream) if stream is not None else None)
+
+    def drain(self):
+        self._capi.call("rplb_sharded_linear_drain", self.handle)
+
+    def close(self):
+        if self.handle:
+            self._capi.load().rplb_sharded_linear_free(self.handle)
+            self.handle = None

@@ -17,6 +17,7 @@ def declared_functions():
     text = re.sub(r"^\s*#.*$", "", text, flags=re.M)
     text = re.sub(r"typedef\s+struct\s*\w*\s*\{.*?\}\s*\w+\s*;", "", text, flags=re.S)
     text = re.sub(r"typedef\s+enum\s*\{.*?\}\s*\w+\s*;", "", text, flags=re.S)
+    text = re.sub(r"typedef\s+[^;{}]*\(\s*\*\s*\w+\s*\)\s*\([^;{}]*\)\s*;", "", text)       # function-pointer types
     names = re.findall(r"\b([A-Za-z_]\w*)\s*\([^;{}]*\)\s*;", text)
     return sorted(set(names))
 

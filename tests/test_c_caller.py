@@ -8,7 +8,8 @@ import pytest
 
 from conftest import ROOT
 
-REF_INCLUDE = os.path.join(os.environ.get("RPL_REFERENCE", "/root/reference"), "include")
+# The reference tree: RPL_REFERENCE, or a checkout named "reference" beside this repository.
+REF_INCLUDE = os.path.join(os.environ.get("RPL_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"), "include")
 SRC = os.path.join(ROOT, "tests", "c", "drop_in_check.c")
 
 
@@ -55,7 +56,7 @@ def test_c_caller_results_match_plain_c_loops(tmp_path, lib, cuda, use_reference
 @pytest.mark.skipif(not os.path.exists(os.path.join(os.path.dirname(REF_INCLUDE), "src", "rpl_nn.c")),
                     reason="reference tree absent")
 def test_combined_library_keeps_the_rest_of_the_reference(tmp_path, lib):
-    """The linking recipe of INTEGRATION.md: the reference's own objects (its INT8
+    """The combined-library linking recipe: the reference's own objects (its INT8
     symbols weakened) next to this library's objects give one library in which the
     fp32 layers are the reference's and the INT8 path is this one."""
     import ctypes as C

@@ -374,3 +374,109 @@ def test_shared_input_forward_like_attention_projections(cuda, lib, port):
     for t in tws + tbs + [th, td, odd]:
         lib.tensor_free(t)
     assert lib.rpl_cuda_last_error() == 0
+
+
+def test_model_quantize_per_channel(cuda, lib, port):
+    """The per-channel model quantizer the reference announces and leaves undone
+    (src/rpl_quantization.c:286-292): weights per row of shape[0], biases with one scale."""
+    from rpl_b200 import capi
+    rng = np.random.default_rng(12)
+    shapes = [(128, 784), (128,), (10, 128), (10,), (4, 3, 8)]
+    arrays = [(rng.standard_normal(s) * 0.05).astype(np.float32) for s in shapes]
+    params = [host_tensor(lib, a) for a in arrays]
+    arr = (C.POINTER(capi.Tensor) * len(params))(*params)
+    qm = C.cast(lib.model_quantize_per_channel(arr, len(params)), C.POINTER(capi.PerChannelQuantizedModel))
+    assert qm and qm.contents.num_params == len(params) and qm.contents.is_quantized
+    for i, a in enumerate(arrays):
+        q = qm.contents.int8_params[i].contents
+        assert q.dims == a.ndim and list(q.shape[:a.ndim]) == list(a.shape)
+        if a.ndim >= 2:
+            wq, ws, _ = port.quantize_per_channel(a, a.shape[0])
+            assert q.num_channels == a.shape[0] and q.channel_size == a.size // a.shape[0]
+        else:
+            wq, s1 = port.quantize_symmetric(a)             # one scale for the whole tensor
+            ws = np.array([s1], np.float32)
+            assert q.num_channels == 1 and q.channel_size == a.size
+        assert same(read_host(q.data, a.shape, np.int8), wq)
+        assert same(read_host(q.scales, (q.num_channels,), np.float32), ws)
+        assert not read_host(q.zero_points, (q.num_channels,), np.int32).any()
+    lib.per_channel_quantized_model_free(qm)
+    # the original entry point keeps ignoring its flag, as the reference does
+    qm2 = lib.model_quantize(arr, len(params), True)
+    wq, ws = port.quantize_symmetric(arrays[0])
+    assert same(np.float32(qm2.contents.int8_params[0].contents.scale), ws)
+    lib.quantized_model_free(qm2)
+    for t in params:
+        lib.tensor_free(t)
+
+
+def test_a_give_up_is_reported_to_the_thread_that_launched_it(cuda, lib, port):
+    """Two host threads: one provokes the bounded-wait give-up and leaves its code in place;
+    the other sees a clear status and runs a tensor-core GEMM; the first then finds its code."""
+    import threading
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(2)
+    A = rng.integers(-128, 128, (128, 256), dtype=np.int8)
+    W = rng.integers(-128, 128, (256, 256), dtype=np.int8)
+    want = port.linear(A, W)
+    seen = {}
+    gave_up, other_done = threading.Event(), threading.Event()
+
+    def first():
+        torch.cuda.set_device(0)
+        st = torch.cuda.Stream()
+        seen["rc"] = lib.rplb_selftest_bounded_wait_keep(C.c_void_p(st.cuda_stream))
+        gave_up.set()
+        other_done.wait(60)
+        seen["first_status"] = D.kernel_status(True)
+        seen["first_after"] = D.kernel_status(False)
+
+    def second():
+        torch.cuda.set_device(0)
+        gave_up.wait(60)
+        seen["second_status"] = D.kernel_status(False)
+        D.gemm_backend(3)                                 # per thread: the tensor-core kernel, 128 x 256 tiles
+        got = D.linear_i8(torch.from_numpy(A).to(cuda), torch.from_numpy(W).to(cuda))
+        torch.cuda.synchronize()
+        seen["second_ok"] = bool(np.array_equal(got.cpu().numpy(), want))
+        seen["second_after"] = D.kernel_status(False)
+        other_done.set()
+
+    t1, t2 = threading.Thread(target=first), threading.Thread(target=second)
+    t1.start(); t2.start(); t1.join(120); t2.join(120)
+    assert seen == {"rc": 0, "second_status": 0, "second_ok": True, "second_after": 0, "first_status": 99, "first_after": 0}
+    assert D.gemm_backend(0) == 0                         # this thread's setting was never touched by the other's
+
+
+def test_scratch_cannot_grow_inside_a_capture(cuda, lib):
+    """A graph keeps the scratch block's address: growing it during capture is refused with an error,
+    and a reservation made beforehand makes the same capture work."""
+    from rpl_b200 import capi, device as D
+    side = torch.cuda.Stream()
+    x = torch.randn(1 << 22, device=cuda)
+    params = torch.empty(8, device=cuda)
+    handle = C.c_void_p(side.cuda_stream)
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g, stream=side, capture_error_mode="relaxed"):
+                with pytest.raises(capi.RplError) as e:
+                    D.minmax(x, params=params)            # this stream has no scratch block yet
+                assert e.value.code == capi.RPLB_E_UNSUPPORTED
+                torch.zeros(1, device=cuda)               # something capturable, so the graph is not empty
+        finally:
+            del g
+    capi.call("rplb_scratch_reserve", handle, 1 << 20)
+    with torch.cuda.stream(side):
+        D.minmax(x, params=params)                        # outside a capture: fine, and now warm
+        side.synchronize()
+        want = params.clone()
+        g = torch.cuda.CUDAGraph()
+        params.zero_()
+        with torch.cuda.graph(g, stream=side):
+            D.minmax(x, params=params)
+        g.replay()
+        side.synchronize()
+    assert torch.equal(params, want)
+    del g
+    capi.call("rplb_scratch_release", handle)

@@ -24,12 +24,16 @@ def host(t):
     return t.detach().cpu().numpy()
 
 
-@pytest.fixture
-def backend():
+@pytest.fixture(params=[0, 1], ids=["tma_store", "register_store"])
+def backend(request):
+    """Every test runs with both store paths of the tensor-core epilogue: 32 x 32 chunks through
+    TMA tensor stores (where the output's alignment allows it) and rows stored from registers."""
     from rpl_b200 import device as D
     prev = D.gemm_backend(0)
+    prev_epi = D.gemm_epilogue(request.param)
     yield D
     D.gemm_backend(prev)
+    D.gemm_epilogue(prev_epi)
     assert D.kernel_status(True) == 0
 
 

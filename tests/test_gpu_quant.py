@@ -203,3 +203,32 @@ def test_near_tie_inputs_and_extreme_parameters(cuda, lib, port):
     qd = dev(q, cuda)
     for scale, zp in ((0.1, 2**21 - 1), (0.1, -(2**21) + 1), (0.1, 2**21), (0.1, -(2**22)), (0.1, 2**31 - 1), (0.1, -2**31), (3e38, 7)):
         assert same(host(D.dequantize(qd, scale, zp)), port.dequantize(q, scale, zp)), (scale, zp)
+
+
+def test_scale_from_a_combined_pair_is_the_single_gpu_scale(cuda, lib, port):
+    """Row-sharded activations: (-min, max) pairs are max-reduced across ranks and the scale is derived
+    from the combined pair.  For a few thousand absmax bit patterns that scale must be the very bits
+    tensor_quantize_int8_symmetric computes (an IEEE division by 127, not a multiplication by 1/127)."""
+    from rpl_b200 import device as D
+    rng = np.random.default_rng(17)
+    vals = np.concatenate([np.abs(rng.standard_normal(1500)).astype(np.float32) * 5,
+                           rng.integers(0x00800000, 0x7F000000, 1500).astype(np.uint32).view(np.float32),
+                           np.array([0.0, 1e-45, 1.1754944e-38, 127.0, 3.4028235e38], np.float32)])
+    params = torch.empty(8, dtype=torch.float32, device=cuda)
+    pair = torch.empty(2, dtype=torch.float32, device=cuda)
+    got_direct, got_pair = [], []
+    for v in vals:
+        x = torch.tensor([float(v), -float(v) / 2, 0.0, float(v) / 4], device=cuda)
+        D.minmax(x, params=params)
+        got_direct.append(params[D.QPARAM_SCALE_SYM].clone())
+        D.qparams_to_pair(params, pair)
+        # what another rank with smaller extremes contributes changes nothing
+        other = torch.tensor([float(v) / 8, float(v) / 3], device=cuda)
+        torch.maximum(pair, other, out=pair)
+        params.zero_()
+        D.qparams_from_pair(pair, params)
+        got_pair.append(params[D.QPARAM_SCALE_SYM].clone())
+    a = torch.stack(got_direct).cpu().numpy()
+    b = torch.stack(got_pair).cpu().numpy()
+    want = np.array([port.scale_symmetric(np.float32(-v / 2), np.float32(v)) for v in vals], np.float32)
+    assert same(a, want) and same(b, want)
