@@ -51,6 +51,7 @@ def parse_args():
                     help="row blocks for pipelining the quantize pass under the GEMM (0 = sequential, "
                          "-1 = choose: pipelined when a rank's GEMM is short enough for the quantize pass to matter)")
     ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 tcgen05 128x256 tiles, 4 CTA pair, 5 256x256 tiles per CTA)")
+    ap.add_argument("--gemm-epilogue", type=int, default=0, help="rplb_gemm_epilogue code (0 TMA tensor stores where possible, 1 stores from registers)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
     ap.add_argument("--gather", action="store_true",
                     help="with N > 1 also time the all-gather of the fp32 column blocks into [M, N] on every rank (own line, not part of value)")
@@ -316,6 +317,7 @@ def run_ours(a):
     peaks = measured_peaks()
     M, N, K = a.m, a.n, a.k
     D.gemm_backend(a.gemm_backend)
+    D.gemm_epilogue(a.gemm_epilogue)
     if a.sweep_only:
         print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks)}), flush=True)
         return

@@ -109,6 +109,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity.  Gives up after about a second
 // (or as soon as another role has given up) and returns false.
 constexpr long long kWaitLimitCycles = 2000000000LL;
+// Rows from another GPU: half of that, so that this wait is the one that runs out
+// (and names the cause) before the roles waiting further down the pipeline do.
+constexpr long long kRowWaitLimitCycles = kWaitLimitCycles / 2;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                                   long long limit = kWaitLimitCycles) {
@@ -146,7 +149,7 @@ __device__ __forceinline__ bool wait_rows_ready(const uint32_t* word, uint32_t e
             __nanosleep(100);
             if ((++spins & 63u) == 0) {
                 if (*abort_flag) return false;
-                if (clock64() - t0 > kWaitLimitCycles) {
+                if (clock64() - t0 > kRowWaitLimitCycles) {
                     *abort_flag = 1;
                     atomicCAS(status, 0, (int)TC_WAIT_ROWS);
                     return false;

@@ -67,10 +67,10 @@ def test_arriving_rows_that_never_arrive_end_in_a_status_code(cuda, lib, port):
     D.linear_i8_dequant_arriving(dev(xq, cuda), dev(wq, cuda), a_scale, dev(ws, cuda), ready, 7, 0, 1)
     torch.cuda.synchronize()
     assert D.kernel_status(False) == 5
+    prev = D.gemm_backend(3)                                # the tensor-core kernel, whatever the size
     with pytest.raises(capi.RplError):                      # refused until the caller has looked
         D.linear_i8_dequant(dev(xq, cuda), dev(wq, cuda), a_scale, dev(ws, cuda))
     assert D.kernel_status(True) == 0
-    prev = D.gemm_backend(3)
     got = D.linear_i8_dequant(dev(xq, cuda), dev(wq, cuda), a_scale, dev(ws, cuda))
     D.gemm_backend(prev)
     assert same(got.cpu().numpy(), port.linear_dequant(xq, wq, np.float32(0.01), ws))
