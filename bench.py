@@ -6,13 +6,18 @@ Workload (default): the large sharded INT8 GEMM, M=65536, K=8192, N=65536.
 A is fp32 ~ N(0,1), quantized per tensor (symmetric) every step; the weight is
 fp32 ~ N(0,0.02) stored [N,K], quantized per output channel once at set-up
 (weights are static) and split over the output columns across the ranks; the
-output is fp32 acc*sA*sW[n], left column-sharded.  One step = quantize(A) +
-GEMM + dequantizing epilogue on every rank; the metric counts 2*M*N*K integer
-operations per step over the whole job ("strong" scaling: N is split).
+output is fp32 acc*sA*sW[n], left column-sharded.  The rows of A are split over
+the ranks too: every rank holds its rows in fp32, the ranks agree on the scale
+with one max-all-reduce, each quantizes its rows and sends the int8 rows to the
+others over NVLink while the GEMM already runs.  One step = that on every rank;
+the metric counts 2*M*N*K integer operations per step over the whole job
+("strong" scaling: the work is split).  The schedule is the same at every N.
 
 Prints one JSON line (rank 0).  `value` is timed with inputs resident in HBM;
-`e2e` repeats the step through the host-buffer API with the host->device copy
-of A and the device->host copy of the output inside the timed region.
+`e2e` repeats the step through the C ABI's host-buffer call with the
+host->device copy of each rank's rows of A and the device->host copy of its
+output block inside the timed region.  After the timed regions samples of the
+results are compared with the CPU oracle (`parity`).
 """
 import argparse
 import json
@@ -45,11 +50,16 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantize/dequantize GB/s figures")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the 512^3 / MLP / projection lines")
+    ap.add_argument("--no-parity", action="store_true", help="skip the checks against the CPU oracle after the timed region")
+    ap.add_argument("--no-probe", action="store_true", help="skip the cuBLASLt INT8 probe (torch._int_mm)")
+    ap.add_argument("--schedule", default="rows", choices=["rows", "replicated"],
+                    help="rows: every rank holds, quantizes and sends only its rows of A (the default at every N); "
+                         "replicated: every rank holds and quantizes all of A (comparison only, N > 1)")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
-    ap.add_argument("--overlap", type=int, default=-1,
-                    help="row blocks for pipelining the quantize pass under the GEMM (0 = sequential, "
-                         "-1 = choose: pipelined when a rank's GEMM is short enough for the quantize pass to matter)")
+    ap.add_argument("--overlap", type=int, default=0,
+                    help="replicated schedule only: row blocks for pipelining the quantize pass under the GEMM (0 = sequential)")
     ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 tcgen05 128x256 tiles, 4 CTA pair, 5 256x256 tiles per CTA)")
     ap.add_argument("--gemm-epilogue", type=int, default=0, help="rplb_gemm_epilogue code (0 TMA tensor stores where possible, 1 stores from registers)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the baseline sample")
@@ -223,7 +233,64 @@ def event_ms(pairs):
     return [a.elapsed_time(b) for a, b in pairs]
 
 
-def quantize_sweep_one(torch, D, dev, peaks, n):
+class Checker:
+    """The CPU oracle as a checker of sampled results: the reference's own compiled code
+    (oracle/_ref) when it is present, else the C restatement.  Never timed, never shipped."""
+
+    def __init__(self):
+        from oracle.loader import Port, Ref, ref_available
+        self.port = Port()
+        self.ref = Ref() if ref_available() else None
+        self.name = "reference" if self.ref is not None else "port"
+        self.checked = 0
+        self.mismatches = 0
+        self.notes = []
+
+    def scale(self, lo, hi):
+        return self.port.scale_symmetric(lo, hi)            # fmaxf(|min|,|max|) / 127.0f, IEEE division
+
+    def quantize(self, x, scale):
+        return (self.ref or self.port).quantize(x, scale, 0)
+
+    def tile(self, xq, wq, scale, ws):
+        """fp32 outputs of int8 rows xq against int8 weight rows wq: accumulate, then (float)acc * sA, then * sW[n]."""
+        import numpy as np
+        if self.ref is not None:
+            acc = self.ref.linear(xq, wq)
+            return (acc.astype(np.float32) * np.float32(scale)) * ws[None, :]
+        return self.port.linear_dequant(xq, wq, scale, ws)
+
+    def expect(self, ok, what):
+        self.checked += 1
+        if not ok:
+            self.mismatches += 1
+            if len(self.notes) < 8:
+                self.notes.append(what)
+
+    def result(self):
+        r = {"checked": self.checked, "mismatches": self.mismatches, "oracle": self.name}
+        if self.notes:
+            r["first_mismatches"] = self.notes
+        return r
+
+
+def check_quantize_windows(torch, chk, x, q, scale_dev, windows, what, seed=7):
+    """`windows` windows of 4096 elements of a quantized tensor against the oracle, plus its scale."""
+    import numpy as np
+    n = x.numel()
+    lo, hi = float(x.min().item()), float(x.max().item())       # exact operations: any device may take them
+    want_scale = chk.scale(np.float32(lo), np.float32(hi))
+    got_scale = np.float32(scale_dev.item())
+    chk.expect(want_scale.tobytes() == got_scale.tobytes(), "%s: scale %r, oracle %r" % (what, got_scale, want_scale))
+    rng = np.random.default_rng(seed)
+    xf, qf = x.reshape(-1), q.reshape(-1)
+    for _ in range(windows):
+        o = int(rng.integers(0, max(1, n - 4096)))
+        xs = xf[o:o + 4096].cpu().numpy()
+        chk.expect(np.array_equal(chk.quantize(xs, want_scale), qf[o:o + 4096].cpu().numpy()), "%s: window at %d" % (what, o))
+
+
+def quantize_sweep_one(torch, D, dev, peaks, n, chk=None):
     """Quantize / dequantize GB/s on n fp32 elements, rows of 4096: N(0,3) with outliers at +/-50."""
     g = torch.Generator(device=dev)
     g.manual_seed(0x5EED0040)
@@ -239,9 +306,10 @@ def quantize_sweep_one(torch, D, dev, peaks, n):
         ("quantize_per_tensor_symmetric", 9.0, lambda: D.quantize_symmetric(x, out=q, params=params)),
         ("minmax", 4.0, lambda: D.minmax(x, params=params)),
         ("quantize_per_channel_rows4096", 5.0, lambda: D.quantize_per_channel(x2, out=q.view(-1, 4096))),
-        # the other reading of "rows of 4096 channels": 4096 channels of n/4096 elements each.  A channel is
-        # read twice by its CTA; the second read comes from L2 while the ~1184 channels in flight fit there
-        # (5 B/element of HBM traffic), otherwise both passes go to HBM (9 B/element).
+        # the other reading of "rows of 4096 channels": 4096 channels of n/4096 elements each.  Channels of up
+        # to 232 KiB are kept on chip (registers + shared memory) and read from HBM once (5 B/element);
+        # longer ones are read twice by their CTA, the second time from L2 while the ~1184 channels in
+        # flight fit there, otherwise from HBM (9 B/element).
         ("quantize_per_channel_4096_channels", 5.0 if (n // 4096) * 4 * 1184 <= 100e6 else 9.0,
          lambda: D.quantize_per_channel(x.view(4096, -1), out=q.view(4096, -1))),
         ("dequantize", 5.0, lambda: D.dequantize(q, 0.3937, 0, out=back)),
@@ -268,16 +336,20 @@ def quantize_sweep_one(torch, D, dev, peaks, n):
         gbs = bytes_per_elem * n / (med * 1e-3) / 1e9
         res[name] = {"ms": med, "gbs": gbs, "bytes_per_elem": bytes_per_elem, "frac": gbs / peaks["hbm_gbs"]}
     res["launches"] = launches
+    if chk is not None and n >= (1 << 26):
+        D.quantize_symmetric(x, out=q, params=params)
+        torch.cuda.synchronize()
+        check_quantize_windows(torch, chk, x, q, params[D.QPARAM_SCALE_SYM], 64, "per-tensor quantize of 2^%d elements" % (n.bit_length() - 1))
     return res
 
 
-def quantize_sweep(torch, D, dev, peaks):
+def quantize_sweep(torch, D, dev, peaks, chk=None):
     """The memory-bound sweep: 2^26 elements (256 MiB, larger than L2) is the quoted
     size; 2^20 (fits in L2: launch- and L2-bound) and 2^30 (4 GiB) ride along."""
-    res = quantize_sweep_one(torch, D, dev, peaks, 1 << 26)
+    res = quantize_sweep_one(torch, D, dev, peaks, 1 << 26, chk)
     res["other_sizes"] = {}
     for n in (1 << 20, 1 << 30):
-        r = quantize_sweep_one(torch, D, dev, peaks, n)
+        r = quantize_sweep_one(torch, D, dev, peaks, n, chk)
         res["other_sizes"][str(n)] = {k: {"ms": v["ms"], "gbs": v["gbs"], "frac": v["frac"]} for k, v in r.items()
                                       if isinstance(v, dict)}
         res["launches"] += r["launches"]
@@ -296,12 +368,143 @@ def smi_id(torch, dev, local):
         return ids[local] if local < len(ids) else str(local)
 
 
+class NearGpu:
+    """While active, the process runs on the CPUs next to its GPU, so that page-locked
+    buffers allocated inside land in that NUMA node's memory (each rank's PCIe traffic
+    then stays off the inter-socket link).  Affinity is put back afterwards; reading
+    NVML's affinity mask changes nothing on the GPU."""
+
+    def __init__(self, torch, dev):
+        self.cpus, self.saved = None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(dev).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+            cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+            allowed = os.sched_getaffinity(0)
+            self.cpus = (cpus & allowed) or None
+        except Exception:
+            self.cpus = None
+
+    def __enter__(self):
+        if self.cpus:
+            try:
+                self.saved = os.sched_getaffinity(0)
+                os.sched_setaffinity(0, self.cpus)
+            except OSError:
+                self.saved = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved:
+            try:
+                os.sched_setaffinity(0, self.saved)
+            except OSError:
+                pass
+
+
+def int8_probe(torch, dev, seconds=2.0):
+    """What the vendor's INT8 GEMM (cuBLASLt through torch._int_mm) reaches on this GPU, 8192^3:
+    best single call and a back-to-back loop of about `seconds` under the power cap.  A ceiling to
+    read the roofline fraction against; it is not on the product path."""
+    n = 8192
+    a = torch.randint(-128, 128, (n, n), device=dev, dtype=torch.int8)
+    b = torch.randint(-128, 128, (n, n), device=dev, dtype=torch.int8)
+    ops = 2.0 * n ** 3
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    reps = max(10, int(seconds * 1e3 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        torch._int_mm(a, b)
+    e1.record()
+    torch.cuda.synchronize()
+    sustained = e0.elapsed_time(e1) / reps
+    return {"burst_tops": ops / (best * 1e-3) / 1e12, "sustained_tops": ops / (sustained * 1e-3) / 1e12, "shape": "8192^3",
+            "what": "torch._int_mm (cuBLASLt INT8) on this GPU in this run, outside the timed region"}
+
+
+def rows_of_a(torch, dev, M, K, r0, rc):
+    """Rows [r0, r0 + rc) of the synthetic activation ~ N(0,1): generated in blocks of 4096 rows, each from
+    its own seed, so that a rank makes exactly its rows and every split of the rows gives the same matrix."""
+    out = torch.empty((rc, K), dtype=torch.float32, device=dev)
+    g = torch.Generator(device=dev)
+    blk = 4096
+    b = r0 // blk
+    while b * blk < r0 + rc:
+        g.manual_seed(0x5EED0050 + 7919 * b)
+        rows = torch.randn((min(blk, M - b * blk), K), device=dev, generator=g)
+        lo, hi = max(r0, b * blk), min(r0 + rc, (b + 1) * blk)
+        out[lo - r0:hi - r0] = rows[lo - b * blk:hi - b * blk]
+        b += 1
+    return out
+
+
+def check_main_results(torch, dist, chk, layer, A_local, out, wq, wsc, M, K, world, rank, dev):
+    """Samples of the timed run's results against the oracle: the agreed scale, windows of this rank's int8
+    rows, the int8 activation as every rank holds it (block checksums must agree across ranks), and 128 x 128
+    tiles of this rank's output block, half of them on rows that came from other ranks."""
+    import numpy as np
+    r0, rc = layer.rows(M)
+    xq, scale_dev = layer.activation(M)
+    lo = torch.tensor([float(A_local.min().item()) if rc else float("inf")], device=dev)
+    hi = torch.tensor([float(A_local.max().item()) if rc else float("-inf")], device=dev)
+    if world > 1:
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    want_scale = chk.scale(np.float32(lo.item()), np.float32(hi.item()))
+    got_scale = np.float32(scale_dev.item())
+    chk.expect(want_scale.tobytes() == got_scale.tobytes(), "activation scale %r, oracle %r" % (got_scale, want_scale))
+    rng = np.random.default_rng(1000 + rank)
+    for _ in range(32 if rc else 0):
+        m, k0 = int(rng.integers(0, rc)), int(rng.integers(0, max(1, K - 4096)))
+        xs = A_local[m, k0:k0 + 4096].cpu().numpy()
+        chk.expect(np.array_equal(chk.quantize(xs, want_scale), xq[r0 + m, k0:k0 + 4096].cpu().numpy()),
+                   "int8 activation, row %d" % (r0 + m))
+    if world > 1:
+        # every rank must hold the same int8 activation: per-row checksums (a plain and a weighted sum of the
+        # row's 8-byte words, modulo 2^64) are compared with rank 0's
+        words = xq.view(-1, K).view(torch.int64) if K % 8 == 0 else xq.view(-1, K).to(torch.int64)
+        wts = torch.arange(words.shape[1], device=dev, dtype=torch.int64) * 2 + 1
+        sums = torch.stack([words.sum(1), (words * wts).sum(1)])
+        ref = sums.clone()
+        dist.broadcast(ref, src=0)
+        chk.expect(bool(torch.equal(ref, sums)), "int8 activation differs from rank 0's copy")
+    count = wq.shape[0]
+    tiles = 64 if world == 1 else 32
+    ws_host = wsc.cpu().numpy()
+    for t in range(tiles if count else 0):
+        if world > 1 and t % 2 == 1 and M > rc:             # rows that arrived from another rank
+            m0 = (r0 + rc + int(rng.integers(0, M - rc - 127))) % M
+            m0 = min(m0, M - 128)
+        else:
+            m0 = r0 + int(rng.integers(0, max(1, rc - 127))) if rc >= 128 else int(rng.integers(0, max(1, M - 127)))
+        n0 = int(rng.integers(0, max(1, count - 127)))
+        rows = min(128, M - m0)
+        want = chk.tile(xq[m0:m0 + rows].cpu().numpy(), wq[n0:n0 + 128].cpu().numpy(), want_scale, ws_host[n0:n0 + 128])
+        got = out[m0:m0 + rows, n0:n0 + 128].cpu().numpy()
+        chk.expect(np.array_equal(got.view(np.uint32), want.view(np.uint32)), "output tile at (%d, %d)" % (m0, n0))
+
+
 def run_ours(a):
     import torch
     import torch.distributed as dist
 
     from rpl_b200 import device as D
-    from rpl_b200.sharded import ShardedQuantizedLinear, shard_range
+    from rpl_b200.sharded import RowShardedLinear, ShardedQuantizedLinear, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -318,8 +521,13 @@ def run_ours(a):
     M, N, K = a.m, a.n, a.k
     D.gemm_backend(a.gemm_backend)
     D.gemm_epilogue(a.gemm_epilogue)
+    chk = None
+    if not a.no_parity:
+        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // max(world, 1)))   # torchrun pins it to 1
+        chk = Checker()
     if a.sweep_only:
-        print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks)}), flush=True)
+        print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks, chk),
+                          "parity": chk.result() if chk else None}), flush=True)
         return
 
     def barrier():
@@ -327,36 +535,50 @@ def run_ours(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- synthetic inputs (same A on every rank; W rows by global index) ----
-    g = torch.Generator(device=dev)
-    g.manual_seed(0x5EED0050)
-    A = torch.randn((M, K), device=dev, generator=g)
+    replicated = a.schedule == "replicated" and world > 1
+    # ---- synthetic inputs: this rank's rows of A (all of A under the replicated schedule), its rows of W ----
     begin, count = shard_range(N, world, rank, 256)
+    r0, rc = (0, M) if replicated else shard_range(M, world, rank, 128)
+    A_local = rows_of_a(torch, dev, M, K, r0, rc)
+    g = torch.Generator(device=dev)
     wq = torch.empty((count, K), dtype=torch.int8, device=dev)
     wsc = torch.empty(count, dtype=torch.float32, device=dev)
     blk = 4096
-    for r0 in range(0, count, blk):
-        r1 = min(count, r0 + blk)
-        g.manual_seed(0x5EED0051 + (begin + r0))
-        w = torch.randn((r1 - r0, K), device=dev, generator=g) * 0.02
+    for c0 in range(0, count, blk):
+        c1 = min(count, c0 + blk)
+        g.manual_seed(0x5EED0051 + (begin + c0))
+        w = torch.randn((c1 - c0, K), device=dev, generator=g) * 0.02
         q, s, _ = D.quantize_per_channel(w)
-        wq[r0:r1] = q
-        wsc[r0:r1] = s
+        wq[c0:c1] = q
+        wsc[c0:c1] = s
     del w, q, s
-    layer = ShardedQuantizedLinear(wq, wsc, None, n_total=N, rank=rank, world=world)
-    if a.overlap < 0:
-        # Measured on one B200 (ms per step, sequential -> pipelined): 8192 columns per
-        # rank (the 8-GPU share) 4.48 -> 4.13 with six row blocks; 16384 columns 8.06 -> 8.20;
-        # 32768 columns 15.3 -> 15.7; all 65536 columns 29.7 -> 30.6.  The blocks cost the
-        # GEMM about as much as they hide except when the GEMM itself is only a few ms.
-        a.overlap = 6 if float(M) * count * K <= 5.0e12 else 0
     out = torch.empty((M, count), dtype=torch.float32, device=dev)
     ops_total = 2.0 * M * N * K
     ops_rank = 2.0 * M * count * K
 
+    if replicated:
+        old = ShardedQuantizedLinear(wq, wsc, None, n_total=N, rank=rank, world=world)
+        layer = None
+
+        def quantize_half():
+            old.quantize_activation(A_local)
+
+        def gemm_half():
+            old.gemm(old._xq, old._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], out=out)
+    else:
+        layer = RowShardedLinear(wq, wsc, None, n_total=N, max_rows=M, rank=rank, world=world)
+
+        def quantize_half():
+            layer.quantize(A_local, M)
+
+        def gemm_half():
+            layer.gemm(M, out)
+
+    def step_fn():
+        quantize_half()
+        gemm_half()
+
     # ---- device-resident timing ----
-    step_fn = (lambda: layer.forward_overlapped(A, out=out, row_chunks=a.overlap)) if a.overlap > 1 else \
-        (lambda: layer.forward(A, out=out))
     for _ in range(max(a.warmup, 3)):
         step_fn()
     torch.cuda.synchronize()
@@ -385,16 +607,12 @@ def run_ours(a):
     sampler.t_begin = time.time()
     launches0 = D.launch_count()
     e0.record()
-    gemm_pairs = []
     for i in range(a.steps):
-        if a.overlap > 1:
-            layer.forward_overlapped(A, out=out, row_chunks=a.overlap, gemm_events=gemm_pairs)
-            continue
         quant_ev[i][0].record()
-        xq, a_scale = layer.quantize_activation(A)
+        quantize_half()
         quant_ev[i][1].record()
         gemm_ev[i][0].record()
-        layer.gemm(xq, a_scale, out=out)
+        gemm_half()
         gemm_ev[i][1].record()
     e1.record()
     barrier()
@@ -409,12 +627,8 @@ def run_ours(a):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
-    if a.overlap > 1:
-        gemm_ms = sum(event_ms(gemm_pairs)) / a.steps
-        quant_ms = max(ms - gemm_ms, 0.0)               # what of the quantize pass is not hidden under the GEMM
-    else:
-        gemm_ms = sum(event_ms(gemm_ev)) / a.steps
-        quant_ms = sum(event_ms(quant_ev)) / a.steps
+    gemm_ms = sum(event_ms(gemm_ev)) / a.steps
+    quant_ms = sum(event_ms(quant_ev)) / a.steps
     per_rank = torch.tensor([gemm_ms, quant_ms, ms], device=dev)
     if world > 1:
         gathered = [torch.empty_like(per_rank) for _ in range(world)]
@@ -424,17 +638,21 @@ def run_ours(a):
         per_rank = per_rank.reshape(1, 3)
     per_rank = [[round(float(v), 4) for v in row] for row in per_rank.cpu()]
 
+    # ---- samples of the results against the oracle (outside every timed region) ----
+    if chk is not None and layer is not None:
+        check_main_results(torch, dist, chk, layer, A_local, out, wq, wsc, M, K, world, rank, dev)
+
     # ---- optional: all-gather of the column blocks, timed on its own ----
     gather = None
-    if a.gather and world > 1:
-        full = layer.gather(out)                            # warm-up: NCCL channels and buffers
+    if a.gather and world > 1 and layer is not None:
+        full = layer.gather(out, M)                         # warm-up: NCCL channels and buffers
         del full
         barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = 3
         g0.record()
         for _ in range(reps):
-            full = layer.gather(out)
+            full = layer.gather(out, M)
             del full
         g1.record()
         barrier()
@@ -445,41 +663,15 @@ def run_ours(a):
                   "GB/s_per_rank_in": received / (float(tg.item()) * 1e-3) / 1e9,
                   "what": "NCCL all-gather of fp32 [M, N/G] blocks plus unpack into row-major [M, N] on every rank"}
 
-    # ---- optional: the same step with the gather fused into the GEMM epilogue ----
-    if a.gather and world > 1:
-        from rpl_b200.sharded import PeerOutput
-        shared = PeerOutput(M, N, dev)
-        for _ in range(2):
-            layer.forward_gathered(A, shared)
-        barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(a.steps):
-            layer.forward_gathered(A, shared)
-        f1.record()
-        barrier()
-        tf = torch.tensor([f0.elapsed_time(f1) / a.steps], device=dev)
-        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-        same_block = bool(torch.equal(shared.local[:256, begin:begin + count], out[:256]))
-        other = (rank + 1) % world
-        ob, oc = shard_range(N, world, other, 256)
-        probe = out[:256, :min(oc, 1024)].contiguous()       # the neighbour's first rows and columns, for a cross-check
-        probes = [torch.empty_like(probe) for _ in range(world)]
-        dist.all_gather(probes, probe)
-        same_remote = bool(torch.equal(shared.local[:256, ob:ob + min(oc, 1024)], probes[other]))
-        gather["fused"] = {"ms_per_step": float(tf.item()), "value": ops_total / (float(tf.item()) * 1e-3) / 1e12, "unit": UNIT,
-                           "what": "quantize + GEMM whose epilogue stores every tile into all ranks' [M, N] buffers over NVLink (peer stores), fences included",
-                           "matches_sharded_run": same_block and same_remote}
-        shared.close()
-        del shared
-
     # ---- end to end through host buffers ----
     e2e = None
-    if not a.no_e2e:
+    if not a.no_e2e and layer is not None:
         xh = oh = None
         try:
-            xh = torch.empty((M, K), dtype=torch.float32, pin_memory=True)
-            oh = torch.empty((M, count), dtype=torch.float32, pin_memory=True)
+            with NearGpu(torch, dev):
+                xh = torch.empty((max(rc, 1), K), dtype=torch.float32, pin_memory=True)
+                oh = torch.empty((M, max(count, 1)), dtype=torch.float32, pin_memory=True)
+                oh.zero_()                                  # touch the pages while the process is near its GPU
             have = 1
         except RuntimeError:
             have = 0
@@ -488,33 +680,24 @@ def run_ours(a):
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN)          # all ranks take the same branch
         if int(agreed.item()) == 0:
             e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                   "error": "page-locked host buffers (%.1f GiB per rank) could not be allocated" % ((M * K + M * count) * 4 / 2**30)}
+                   "error": "page-locked host buffers (%.1f GiB per rank) could not be allocated" % ((rc * K + M * count) * 4 / 2**30)}
         else:
-            xh.copy_(A)
+            if rc:
+                xh[:rc].copy_(A_local)
             torch.cuda.synchronize()
-            # The reference-facing C ABI with host buffers: a QuantizedLinear layer over this rank's
-            # device-resident int8 weights, quantized_linear_submit_host / _drain.  Every call uploads
-            # its whole activation and downloads its whole output; the upload of call n+1 overlaps the
-            # download of call n (PCIe is full duplex).  Quantize and GEMM run on torch's current
-            # stream, which after the drain has also waited for the downloads, so the events see it all.
-            import ctypes as C
-            from rpl_b200 import capi
-            L = capi.load()
-            clayer = L.quantized_linear_wrap(wq.data_ptr(), wsc.data_ptr(), None, K, count)
-            if not clayer:
-                raise RuntimeError("quantized_linear_wrap failed")
-            estream = torch.cuda.Stream(device=dev)         # quantize and GEMM of the e2e calls run here
+            # The C ABI's host-buffer call (rplb_sharded_linear_submit_host / _drain): every call uploads this
+            # rank's rows of A and downloads its whole output block, row block by row block while the next
+            # block computes; the upload of call n+1 overlaps the download of call n (PCIe is full duplex).
+            # Quantize and GEMM run on `estream`, which after the drain has also waited for the downloads,
+            # so the events see it all.
+            estream = torch.cuda.Stream(device=dev)
             estream.wait_stream(torch.cuda.current_stream())
-            main = C.c_void_p(estream.cuda_stream)
 
             def submit():
-                rc = L.quantized_linear_submit_host(clayer, xh.data_ptr(), M, oh.data_ptr(), False, main)
-                if rc != 0:
-                    raise RuntimeError("quantized_linear_submit_host failed with %d" % rc)
+                layer.submit_host(xh, M, oh, row_blocks=8, stream=estream)
 
             submit()
-            if L.quantized_linear_drain(clayer) != 0:
-                raise RuntimeError("quantized_linear_drain failed")
+            layer.drain()
             esteps = max(2, min(a.steps, 6))
             barrier()
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -522,22 +705,38 @@ def run_ours(a):
             s0.record(estream)
             for _ in range(esteps):
                 submit()
-            if L.quantized_linear_drain(clayer) != 0:
-                raise RuntimeError("quantized_linear_drain failed")
+            layer.drain()
             s1.record(estream)
             barrier()
             e2e_launches = D.launch_count() - launches_e0
             te = torch.tensor([s0.elapsed_time(s1) / esteps], device=dev)
             if world > 1:
                 dist.all_reduce(te, op=dist.ReduceOp.MAX)
-            same = bool(torch.equal(oh[:256].to(dev), out[:256]))
+            same = bool(torch.equal(oh[:256].to(dev), out[:256])) and bool(torch.equal(oh[M - 256:].to(dev), out[M - 256:]))
+            if chk is not None:
+                chk.expect(same, "host-buffer call differs from the device-resident run")
             e2e = {"value": ops_total / (float(te.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(te.item()),
-                   "steps": esteps, "h2d_bytes_per_step": int(M * K * 4) * world, "d2h_bytes_per_step": int(M * N * 4),
-                   "api": "quantized_linear_submit_host / quantized_linear_drain (C ABI, page-locked host buffers)",
+                   "steps": esteps, "h2d_bytes_per_step": int(M * K * 4), "d2h_bytes_per_step": int(M * N * 4),
+                   "api": "rplb_sharded_linear_submit_host / rplb_sharded_linear_drain (C ABI, page-locked host buffers; "
+                          "every rank uploads its own rows of A and downloads its own output columns)",
                    "matches_device_run": same, "gpu_launches": int(e2e_launches)}
-            L.quantized_linear_free(clayer)
         del xh, oh
 
+    parity = None
+    if chk is not None:
+        counts = torch.tensor([chk.checked, chk.mismatches], device=dev)
+        if world > 1:
+            dist.all_reduce(counts)
+        parity = chk.result()
+        parity["checked"], parity["mismatches"] = int(counts[0].item()), int(counts[1].item())
+        parity["what"] = ("per rank: the agreed scale, 32 windows of the int8 activation, per-block checksums of the whole int8 "
+                          "activation against rank 0's, %d output tiles of 128 x 128 (half on rows received from other ranks), "
+                          "and the host-buffer result against the device-resident one" % (64 if world == 1 else 32))
+
+    if layer is not None:
+        if world > 1:
+            dist.barrier()
+        layer.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -545,35 +744,57 @@ def run_ours(a):
 
     # DRAM traffic of the GEMM from an ncu capture at 16384 x 16384 x 8192
     # (dram read + write): 6.99 B per output element at K = 8192.
-    gemm_launches_per_step = max(1, len(gemm_pairs) // max(a.steps, 1)) if a.overlap > 1 else 1
-    traffic = 6.99 * M * count / gemm_launches_per_step if K == 8192 else None
+    traffic = 6.99 * M * count if K == 8192 else None
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
+    sched = ("every rank: min/max of its rows, max-all-reduce of (-min, max), quantize its rows, peer copies of the int8 rows "
+             "to the other ranks under the GEMM, GEMM over all rows (waits per 128-row block)") if not replicated else \
+        "replicated A: every rank quantizes all rows (comparison schedule)"
     line = {
         "metric": METRIC, "value": ops_total / (ms_max * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": workload_name(a), "parallelism": "N-split over %d rank(s), output left column-sharded" % world,
-                   "columns_per_rank": count,
-                   "schedule": ("quantize pass pipelined under the GEMM in %d row blocks" % a.overlap) if a.overlap > 1
-                   else "min/max, quantize, GEMM one after the other", "l2": "no flush: per-step inputs and outputs exceed L2 (A %.1f GiB fp32, out %.1f GiB per rank)"
-                   % (M * K * 4 / 2**30, M * count * 4 / 2**30)},
-        "breakdown_ms": {"quantize_A": quant_ms, "gemm_with_epilogue": gemm_ms,
+        "config": {"workload": workload_name(a), "parallelism": "output columns and activation rows split over %d rank(s), output left column-sharded" % world,
+                   "columns_per_rank": count, "rows_per_rank": rc, "schedule": sched,
+                   "l2": "no flush: per-step inputs and outputs exceed L2 (A rows %.2f GiB fp32, int8 A %.2f GiB, out %.1f GiB per rank)"
+                   % (rc * K * 4 / 2**30, M * K / 2**30, M * count * 4 / 2**30)},
+        "breakdown_ms": {"quantize_A_and_scale_agreement": quant_ms, "gemm_with_epilogue": gemm_ms,
                          "per_rank_gemm_quant_step": per_rank},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by output elements)",
-                     "algorithmic_bytes": float(M * K + count * K + 4 * M * count) / gemm_launches_per_step,
-                     "launches_per_step": gemm_launches_per_step, "kernel": "gemm_i8_tc_kernel",
+                     "algorithmic_bytes": float(M * K + count * K + 4 * M * count),
+                     "launches_per_step": 1, "kernel": "gemm_i8_tc_kernel",
                      "peak_note": "2 x bf16_tflops_sustained of %s (int8 dense = 2 x bf16 dense)" % peaks["source"],
-                     "frac_of_nominal_4500": achieved / 4500.0},
-        "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
+                     "frac_of_nominal_4500": achieved / 4500.0,
+                     "ms_x_mhz": gemm_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None},
+        "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "parity": parity,
     }
     if gather is not None:
         line["gather"] = gather
+    del A_local, out
+    torch.cuda.empty_cache()
     if world == 1 and not a.no_sweep:
-        line["quantize_sweep"] = quantize_sweep(torch, D, dev, peaks)
+        line["quantize_sweep"] = quantize_sweep(torch, D, dev, peaks, chk)
+        if chk is not None:
+            line["parity"].update(chk.result())
+    if world == 1 and not a.no_secondary:
+        del wq, wsc
+        torch.cuda.empty_cache()
+        line["secondary"] = {}
+        for wl in ("c1", "c2", "c3"):
+            b = argparse.Namespace(**vars(a))
+            b.workload, b.steps = wl, 50 if wl != "c3" else 10
+            line["secondary"][wl] = secondary_line(torch, D, dev, peaks, b, chk)
+            torch.cuda.empty_cache()
+        if chk is not None:
+            line["parity"].update(chk.result())
+    if world == 1 and not a.no_probe:
+        # Last of the GPU legs: seconds of dense tensor work leave the board at its power cap, which the
+        # memory-bound figures above must not inherit.
+        line["roofline"]["int8_probe"] = int8_probe(torch, dev)
+        p = line["roofline"]["int8_probe"]
+        p["frac_of_probe_sustained"] = achieved / p["sustained_tops"]
     if world == 1 and not a.no_cpu:
-        del A, out
         cpu = CpuPath(K, a.cpu_seconds)
         cpu.step()
         t0 = time.perf_counter()
@@ -586,18 +807,46 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
-def run_secondary(a):
-    """Secondary configurations on one GPU: device-resident timing, same metric."""
-    import torch
+def timed_replay(torch, D, dev, step, steps, warmup):
+    """ms per step of `step` replayed from a CUDA graph (these steps are a handful of short kernels: the
+    host's launch cost must not show up as GPU idle time), and the library's launches per step."""
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(warmup, 3)):                     # also sizes the library's scratch block of this stream
+            step()
+    side.synchronize()
+    l0 = D.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    per_step = D.launch_count() - l0
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if D.kernel_status(True) != 0:
+        raise RuntimeError("the tcgen05 kernel reported an expired wait")
+    return e0.elapsed_time(e1) / steps, per_step
 
-    from rpl_b200 import device as D
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    peaks = measured_peaks()
-    D.gemm_backend(a.gemm_backend)
+
+def secondary_line(torch, D, dev, peaks, a, chk=None):
+    """One of the smaller configurations on one GPU: device-resident timing, same metric; where the
+    configuration is what a drop-in user calls with host buffers (512^3), that call is timed too."""
+    import ctypes as C
+
+    import numpy as np
+
+    from rpl_b200 import capi
     g = torch.Generator(device=dev)
     g.manual_seed(0x5EED0000 + int(a.workload[1]) * 16)
     one = lambda p: p[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+    extra = {}
     if a.workload == "c1":
         name = "INT8 GEMM 512x512x512: A, B fp32 N(0,1), both per-tensor symmetric, fp32 out acc*sA*sB"
         A = torch.randn((512, 512), device=dev, generator=g)
@@ -612,6 +861,36 @@ def run_secondary(a):
             D.quantize_symmetric(A, out=aq, params=pa)
             D.linear_i8_dequant(aq, bq, one(pa), ws, out=out)
         note = "launch-latency bound: 0.27 GOP is ~0.1 us of tensor work"
+        # The call a drop-in user makes: gemm_int8(A, B, C, 512, 512, 512, ...) of the reference's API with
+        # host buffers (upload, kernel, download, synchronize), beside the reference's CPU code on the same bytes.
+        L = capi.load()
+        rng = np.random.default_rng(0x5EED0010)
+        Ah = rng.integers(-127, 128, (512, 512), dtype=np.int8)
+        Bh = rng.integers(-127, 128, (512, 512), dtype=np.int8)
+        Ch = np.zeros((512, 512), np.int32)
+        args = (Ah.ctypes.data, Bh.ctypes.data, Ch.ctypes.data, 512, 512, 512, 0.011, 0.013, 0.37, 0, 0)
+        for _ in range(5):
+            L.gemm_int8(*args)
+        ts = []
+        for _ in range(30):
+            t0 = time.perf_counter()
+            L.gemm_int8(*args)
+            ts.append(time.perf_counter() - t0)
+        ts.sort()
+        extra["gemm_int8_host_call"] = {"ms": ts[len(ts) // 2] * 1e3, "gops": ops / ts[len(ts) // 2] / 1e9,
+                                        "what": "gemm_int8 of the reference's C API, host buffers in and out, per call (median of 30)"}
+        if chk is not None:
+            cpu = chk.ref or chk.port
+            cpu.gemm_requant(Ah, Bh, 0.011, 0.013, 0.37)
+            tc = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                want = cpu.gemm_requant(Ah, Bh, 0.011, 0.013, 0.37)
+                tc.append(time.perf_counter() - t0)
+            tc.sort()
+            extra["gemm_int8_cpu_" + chk.name] = {"ms": tc[len(tc) // 2] * 1e3, "gops": ops / tc[len(tc) // 2] / 1e9,
+                                                  "cores": chk.port.num_threads()}
+            chk.expect(np.array_equal(Ch, want), "512^3 gemm_int8 through the C API")
     elif a.workload == "c2":
         name = "quantized MLP 784->128->10, batch 65536: X U[0,1) per tensor, W N(0,0.05) per channel, ReLU, fp32 logits"
         Bn = 65536
@@ -621,16 +900,13 @@ def run_secondary(a):
         b1 = torch.randn(128, device=dev, generator=g) * 0.05
         b2 = torch.randn(10, device=dev, generator=g) * 0.05
         xq, px = torch.empty((Bn, 784), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
-        h, hq, ph = torch.empty((Bn, 128), device=dev), torch.empty((Bn, 128), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
+        h, hq = torch.empty((Bn, 128), device=dev), torch.empty((Bn, 128), dtype=torch.int8, device=dev)
         logits = torch.empty((Bn, 10), device=dev)
         ops = 2.0 * Bn * (784 * 128 + 128 * 10)
         # X read twice (min/max, quantize) + int8 X written and read + hidden fp32 written and read once,
         # int8 hidden written and read + logits
         hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4 + 1 + 1) + 10 * 4)
-
         stats = torch.empty(2, device=dev)
-        import ctypes as C
-        from rpl_b200 import capi
 
         def step():
             D.quantize_symmetric(X, out=xq, params=px)
@@ -643,50 +919,45 @@ def run_secondary(a):
             D.linear_i8_dequant(hq, w2q, stats[1:2], w2s, b2, relu=False, out=logits)
         note = "HBM-bound: 13.3 GOP over ~0.7 GB of traffic"
     else:
-        name = "transformer projections: tokens 32768 x d_model 4096, Q/K/V/O weights 4096x4096 per channel, bias, fp32 out"
+        name = ("transformer projections: tokens 32768 x d_model 4096, Q/K/V as one GEMM with N = 12288 plus O (N = 4096), "
+                "weights per channel, bias, fp32 out")
         T, Dm = 32768, 4096
         X = torch.randn((T, Dm), device=dev, generator=g)
         ws_ = [D.quantize_per_channel(torch.randn((Dm, Dm), device=dev, generator=g) * 0.02) for _ in range(4)]
         bs = [torch.randn(Dm, device=dev, generator=g) * 0.02 for _ in range(4)]
-        outs = [torch.empty((T, Dm), device=dev) for _ in range(4)]
+        wqkv = torch.cat([w[0] for w in ws_[:3]]).contiguous()                      # [12288, 4096] int8
+        sqkv = torch.cat([w[1] for w in ws_[:3]]).contiguous()
+        bqkv = torch.cat(bs[:3]).contiguous()
+        qkv = torch.empty((T, 3 * Dm), device=dev)
+        o = torch.empty((T, Dm), device=dev)
         xq, px = torch.empty((T, Dm), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
         ops, hbm_bytes = 4 * 2.0 * T * Dm * Dm, None
 
         def step():
             D.quantize_symmetric(X, out=xq, params=px)
-            for (wq, wsc, _), b, o in zip(ws_, bs, outs):
-                D.linear_i8_dequant(xq, wq, one(px), wsc, b, out=o)
-        note = "X quantized once per step, four GEMMs with fused per-channel dequant + bias"
-    # These steps are a handful of short kernels: replay them from a CUDA graph so
-    # that the host's launch cost does not show up as GPU idle time.  The library
-    # allocates its per-stream scratch on first use, so warm up on the capture stream.
-    side = torch.cuda.Stream(device=dev)
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(max(a.warmup, 3)):
-            step()
-    side.synchronize()
-    l0 = D.launch_count()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
+            D.linear_i8_dequant(xq, wqkv, one(px), sqkv, bqkv, out=qkv)
+            D.linear_i8_dequant(xq, ws_[3][0], one(px), ws_[3][1], bs[3], out=o)
+        note = "X quantized once per step; Q/K/V in one launch (N = 12288), O in a second; fused per-channel dequant + bias"
+    ms, per_step = timed_replay(torch, D, dev, step, a.steps, a.warmup)
+    if a.workload == "c3" and chk is not None:
+        # tiles of the fused Q/K/V output and of O against the oracle
         step()
-    per_step = D.launch_count() - l0
-    for _ in range(3):
-        graph.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.steps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    if D.kernel_status(True) != 0:
-        raise RuntimeError("the tcgen05 kernel reported an expired wait")
-    ms = e0.elapsed_time(e1) / a.steps
+        torch.cuda.synchronize()
+        sa = np.float32(px[D.QPARAM_SCALE_SYM].item())
+        rng = np.random.default_rng(3)
+        for t in range(12):
+            m0 = int(rng.integers(0, T - 128))
+            wmat, smat, bvec, res = (wqkv, sqkv, bqkv, qkv) if t < 9 else (ws_[3][0], ws_[3][1], bs[3], o)
+            n0 = int(rng.integers(0, wmat.shape[0] - 128))
+            want = chk.tile(xq[m0:m0 + 128].cpu().numpy(), wmat[n0:n0 + 128].cpu().numpy(), sa, smat[n0:n0 + 128].cpu().numpy())
+            want = want + bvec[n0:n0 + 128].cpu().numpy()[None, :]
+            got = res[m0:m0 + 128, n0:n0 + 128].cpu().numpy()
+            chk.expect(np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32)), "projection tile (%d, %d)" % (m0, n0))
     line = {"metric": METRIC, "value": ops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1, "steps": a.steps,
             "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": {"workload": name, "note": note, "replay": "CUDA graph of one step"},
             "gpu_launches": int(per_step * a.steps)}
+    line.update(extra)
     if hbm_bytes:
         gbs = hbm_bytes / (ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -695,6 +966,22 @@ def run_secondary(a):
         t = ops / (ms * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "achieved": t, "peak": 2.0 * peaks["bf16_sustained"], "unit": "TOP/s",
                             "frac": t / (2.0 * peaks["bf16_sustained"]), "traffic": None}
+    return line
+
+
+def run_secondary(a):
+    """`--workload c1|c2|c3` on its own: one JSON line for that configuration."""
+    import torch
+
+    from rpl_b200 import device as D
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    D.gemm_backend(a.gemm_backend)
+    D.gemm_epilogue(a.gemm_epilogue)
+    chk = None if a.no_parity else Checker()
+    line = secondary_line(torch, D, dev, measured_peaks(), a, chk)
+    if chk is not None:
+        line["parity"] = chk.result()
     print(json.dumps(line), flush=True)
 
 

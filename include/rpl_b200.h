@@ -245,6 +245,14 @@ int  rplb_quantize_asymmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb
 int  rplb_quantize_per_channel_f32_i8(const float* x, int8_t* q, float* scales, int32_t* zero_points,
                                       uint64_t num_channels, uint64_t channel_size, void* stream);
 
+/* How rplb_quantize_per_channel_f32_i8 treats channels of 32 to 232 KiB (8192
+ * to 59392 floats) for the calling thread: 1 (default) = the channel is kept on
+ * chip (part in registers, the rest staged in shared memory by bulk copies) and
+ * read from HBM once, 0 = two passes over the channel (the second normally
+ * served by L2).  Same results; for measurements.
+ * Returns the previous setting. */
+int  rplb_per_channel_staging(int which);
+
 /* tensor_dequantize_int8 (src/ops_extended.c:67-70): out = (float)(q - zp) * scale. */
 int  rplb_dequantize_i8_f32(const int8_t* q, float* out, uint64_t n, float scale, int32_t zero_point, void* stream);
 

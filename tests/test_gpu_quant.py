@@ -101,18 +101,24 @@ def test_misaligned_views_take_the_scalar_path(cuda, lib, port):
 
 @pytest.mark.parametrize("shape", [(1, 4), (10, 128), (128, 784), (7, 1031), (64, 4096), (5, 8192), (3, 8196),
                                    (2, 40000), (300, 12), (4, 1 << 18),
-                                   # long rows (the two-pass kernel), ragged lengths included
-                                   (5, 16384), (300, 8200), (3, 20000), (4, 65536), (40, 65540), (2, 100000),
+                                   # rows kept on chip in registers + shared memory (32 to 232 KiB), ragged lengths included
+                                   (5, 16384), (300, 8200), (700, 16384), (9, 18432), (7, 18428), (450, 12292),
+                                   (3, 20000), (310, 28672), (149, 24004), (4, 59392), (40, 32768),
+                                   # long rows (the two-pass kernel)
+                                   (3, 59396), (4, 65536), (40, 65540), (2, 100000),
                                    (37, 131072), (3, 262144), (2, 262148), (2, 300000)])
 def test_per_channel_shapes(cuda, lib, port, shape):
-    from rpl_b200 import device as D
+    from rpl_b200 import capi, device as D
     rng = np.random.default_rng(shape[0] * 7919 + shape[1])
     x = sweep_tensor(rng, shape)
     if shape[0] > 2:
         x[1] = 0.0                                   # an all-zero channel: scale 0, every value -128
-    q, sc, zp = D.quantize_per_channel(dev(x, cuda))
     wq, wsc, wzp = port.quantize_per_channel(x, shape[0])
-    assert same(host(sc), wsc) and same(host(zp), wzp) and same(host(q), wq)
+    for staging in (1, 0):                           # rows of 32 to 232 KiB: kept on chip, or two passes
+        prev = capi.load().rplb_per_channel_staging(staging)
+        q, sc, zp = D.quantize_per_channel(dev(x, cuda))
+        capi.load().rplb_per_channel_staging(prev)
+        assert same(host(sc), wsc) and same(host(zp), wzp) and same(host(q), wq), staging
     assert same(host(D.dequantize_per_channel(q, sc)), port.dequantize_per_channel(wq, wsc))
 
 

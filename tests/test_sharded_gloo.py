@@ -68,3 +68,60 @@ def test_two_ranks_ragged_split(tmp_path):
 
 def test_two_ranks_one_empty(tmp_path):
     _run(200, tmp_path)            # a single 256-column unit: rank 1 owns nothing
+
+
+# ---------------------------------------------------------------------------- rows of the activation split over ranks
+def _rows_worker(rank, world, port, M, result_dir):
+    """The row-sharded protocol of rplb_sharded_linear_forward with the CPU checker standing in for the kernels:
+    local min/max, max-all-reduce of (-min, max), scale from the combined pair, local quantize, exchange of the
+    int8 rows.  Every rank must end up with the int8 activation and scale a single rank computes."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle.loader import Port
+        from rpl_b200.sharded import shard_range
+        P = Port()
+        K = 48
+        x = (np.random.default_rng(M).standard_normal((M, K)) * 2.5).astype(np.float32)     # same on every rank
+        r0, rc = shard_range(M, world, rank, 128)
+        mine = x[r0:r0 + rc]
+        lo, hi = (P.minmax_seeded(mine) if rc else (np.float32(np.inf), np.float32(-np.inf)))
+        pair = torch.tensor([-float(lo), float(hi)], dtype=torch.float32)
+        dist.all_reduce(pair, op=dist.ReduceOp.MAX)
+        scale = P.scale_symmetric(np.float32(-pair[0].item()), np.float32(pair[1].item()))
+        q_mine = P.quantize(mine, scale, 0) if rc else np.zeros((0, K), np.int8)
+        # exchange: every rank places its rows at their offset (the peer copies of the GPU path)
+        pieces = [None] * world
+        dist.all_gather_object(pieces, (r0, q_mine))
+        full = np.zeros((M, K), np.int8)
+        covered = 0
+        for b, rows in pieces:
+            full[b:b + rows.shape[0]] = rows
+            covered += rows.shape[0]
+        want_q, want_s = P.quantize_symmetric(x)
+        ok = covered == M and want_s == scale and np.array_equal(full, want_q)
+        # rows are dealt in multiples of 128 (one arrival word per block), contiguous and in rank order
+        ok = ok and (rc == 0 or r0 % 128 == 0) and (rc % 128 == 0 or r0 + rc == M)
+        np.save(os.path.join(result_dir, "rows%d.npy" % rank), np.array([ok]))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_rows(M, tmp_path):
+    world = 2
+    mp.spawn(_rows_worker, args=(world, _free_port(), M, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert np.load(os.path.join(str(tmp_path), "rows%d.npy" % r)).all(), "rank %d" % r
+
+
+def test_row_sharded_quantize_even(tmp_path):
+    _run_rows(1024, tmp_path)
+
+
+def test_row_sharded_quantize_ragged(tmp_path):
+    _run_rows(1100, tmp_path)          # 9 blocks of 128 rows: 5 and 4, the last one ragged
+
+
+def test_row_sharded_quantize_one_rank_without_rows(tmp_path):
+    _run_rows(100, tmp_path)           # a single block: rank 1 contributes the neutral pair (-inf, -inf)
