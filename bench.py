@@ -642,6 +642,22 @@ def run_ours(a):
     if chk is not None and layer is not None:
         check_main_results(torch, dist, chk, layer, A_local, out, wq, wsc, M, K, world, rank, dev)
 
+    # ---- every element of the full-size output: the tensor-core kernel against the dp4a kernel ----
+    if chk is not None and layer is not None and world == 1 and count:
+        try:
+            other = torch.empty_like(out)
+        except RuntimeError:
+            other = None
+        if other is not None:
+            xq_all, scale_dev = layer.activation(M)
+            D.gemm_backend(1)
+            D.linear_i8_dequant(xq_all, wq, scale_dev, wsc, out=other)
+            D.gemm_backend(a.gemm_backend)
+            torch.cuda.synchronize()
+            chk.expect(bool(torch.equal(other, out)), "tcgen05 and dp4a kernels disagree somewhere in the %d x %d output" % (M, count))
+            del other
+            torch.cuda.empty_cache()
+
     # ---- optional: all-gather of the column blocks, timed on its own ----
     gather = None
     if a.gather and world > 1 and layer is not None:
@@ -731,7 +747,8 @@ def run_ours(a):
         parity["checked"], parity["mismatches"] = int(counts[0].item()), int(counts[1].item())
         parity["what"] = ("per rank: the agreed scale, 32 windows of the int8 activation, per-block checksums of the whole int8 "
                           "activation against rank 0's, %d output tiles of 128 x 128 (half on rows received from other ranks), "
-                          "and the host-buffer result against the device-resident one" % (64 if world == 1 else 32))
+                          "the host-buffer result against the device-resident one%s" % (64 if world == 1 else 32, "; every element of the output against "
+                          "the dp4a kernel's" if world == 1 else ""))
 
     if layer is not None:
         if world > 1:
@@ -835,6 +852,62 @@ def timed_replay(torch, D, dev, step, steps, warmup):
     return e0.elapsed_time(e1) / steps, per_step
 
 
+def layers_through_c_api(torch, capi, C, dev, shapes, X, reps, what, shared=False):
+    """ms per pass of quantized Linear layers driven through the reference-style C objects (quantized_linear_create /
+    _forward / _forward_shared_input) on device-resident tensors: what a C caller of the layer API pays per call."""
+    L = capi.load()
+
+    def dev_tensor(t):
+        shape = (C.c_uint32 * t.dim())(*t.shape)
+        p = L.tensor_create_device(t.dim(), shape)
+        capi.call("rplb_copy", C.c_void_p(p.contents.data), C.c_void_p(t.data_ptr()), t.numel() * 4, None)
+        return p
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)
+    layers = []
+    for (n_out, n_in, _) in shapes:
+        w = dev_tensor(torch.randn((n_out, n_in), device=dev, generator=g) * 0.05)
+        b = dev_tensor(torch.randn(n_out, device=dev, generator=g) * 0.05)
+        capi.call("rplb_stream_sync", None)
+        layers.append(L.quantized_linear_create(w, b))
+        L.tensor_free(w)
+        L.tensor_free(b)
+    x = dev_tensor(X)
+    capi.call("rplb_stream_sync", None)
+
+    def one_pass():
+        if shared:
+            arr = (C.c_void_p * len(layers))(*layers)
+            outs = (C.POINTER(capi.Tensor) * len(layers))()
+            if L.quantized_linear_forward_shared_input(arr, len(layers), x, outs, False) != 0:
+                raise RuntimeError("quantized_linear_forward_shared_input failed")
+            for o in outs:
+                L.tensor_free(o)
+        else:
+            cur = x
+            for layer, (_, _, relu) in zip(layers, shapes):
+                nxt = L.quantized_linear_forward(layer, cur, relu)
+                if not nxt:
+                    raise RuntimeError("quantized_linear_forward failed")
+                if cur is not x:
+                    L.tensor_free(cur)
+                cur = nxt
+            L.tensor_free(cur)
+
+    one_pass()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        one_pass()
+        ts.append(time.perf_counter() - t0)
+    ts.sort()
+    for layer in layers:
+        L.quantized_linear_free(layer)
+    L.tensor_free(x)
+    return {"ms": ts[len(ts) // 2] * 1e3, "what": what}
+
+
 def secondary_line(torch, D, dev, peaks, a, chk=None):
     """One of the smaller configurations on one GPU: device-resident timing, same metric; where the
     configuration is what a drop-in user calls with host buffers (512^3), that call is timed too."""
@@ -879,6 +952,20 @@ def secondary_line(torch, D, dev, peaks, a, chk=None):
         ts.sort()
         extra["gemm_int8_host_call"] = {"ms": ts[len(ts) // 2] * 1e3, "gops": ops / ts[len(ts) // 2] / 1e9,
                                         "what": "gemm_int8 of the reference's C API, host buffers in and out, per call (median of 30)"}
+        # linear_int8 of the reference's API on device-resident int8 tensors (the call synchronises before it returns)
+        qa, qb = capi.QuantizedTensor(), capi.QuantizedTensor()
+        qa.data, qb.data = aq.data_ptr(), bq.data_ptr()
+        acc = torch.empty((512, 512), dtype=torch.int32, device=dev)
+        for _ in range(5):
+            L.linear_int8(C.byref(qa), C.byref(qb), None, C.c_void_p(acc.data_ptr()), 512, 512, 512)
+        ts = []
+        for _ in range(50):
+            t0 = time.perf_counter()
+            L.linear_int8(C.byref(qa), C.byref(qb), None, C.c_void_p(acc.data_ptr()), 512, 512, 512)
+            ts.append(time.perf_counter() - t0)
+        ts.sort()
+        extra["linear_int8_device_call"] = {"us": ts[len(ts) // 2] * 1e6,
+                                            "what": "linear_int8 of the reference's C API, device-resident operands, launch + synchronize per call (median of 50)"}
         if chk is not None:
             cpu = chk.ref or chk.port
             cpu.gemm_requant(Ah, Bh, 0.011, 0.013, 0.37)
@@ -900,24 +987,28 @@ def secondary_line(torch, D, dev, peaks, a, chk=None):
         b1 = torch.randn(128, device=dev, generator=g) * 0.05
         b2 = torch.randn(10, device=dev, generator=g) * 0.05
         xq, px = torch.empty((Bn, 784), dtype=torch.int8, device=dev), torch.empty(8, device=dev)
-        h, hq = torch.empty((Bn, 128), device=dev), torch.empty((Bn, 128), dtype=torch.int8, device=dev)
+        h = torch.empty((Bn, 128), device=dev)
         logits = torch.empty((Bn, 10), device=dev)
         ops = 2.0 * Bn * (784 * 128 + 128 * 10)
-        # X read twice (min/max, quantize) + int8 X written and read + hidden fp32 written and read once,
-        # int8 hidden written and read + logits
-        hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4 + 1 + 1) + 10 * 4)
+        # X read twice (min/max, quantize) + int8 X written and read + hidden fp32 written and read once
+        # (its quantize rides inside the last layer: no int8 copy of it) + logits
+        hbm_bytes = Bn * (784 * (4 + 4 + 1 + 1) + 128 * (4 + 4) + 10 * 4)
         stats = torch.empty(2, device=dev)
 
         def step():
             D.quantize_symmetric(X, out=xq, params=px)
-            # layer 1: fused dequant + bias + ReLU; the epilogue also reports max|h| and the scale of h
+            # layer 1 (the kernel for few output features): fused dequant + bias + ReLU; the epilogue also
+            # reports max|h| and the scale of h
             capi.call("rplb_linear_i8_dequant_f32_absmax", C.c_void_p(xq.data_ptr()), C.c_void_p(w1q.data_ptr()),
                       C.c_void_p(h.data_ptr()), Bn, 784, 128, 128, C.c_void_p(one(px).data_ptr()),
                       C.c_void_p(w1s.data_ptr()), C.c_void_p(b1.data_ptr()), 1, C.c_void_p(stats[0:1].data_ptr()),
                       C.c_void_p(stats[1:2].data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
-            D.quantize_dev(h, stats[1:2], out=hq)
-            D.linear_i8_dequant(hq, w2q, stats[1:2], w2s, b2, relu=False, out=logits)
-        note = "HBM-bound: 13.3 GOP over ~0.7 GB of traffic"
+            # layer 2: h is quantized with that scale on its way into the contraction (N = 10: dp4a kernel)
+            D.quantize_linear_dequant(h, w2q, stats[1:2], w2s, b2, relu=False, out=logits)
+        note = "HBM-bound: 13.3 GOP over ~0.6 GB of traffic; three kernels after the min/max pass"
+        extra["c_api"] = layers_through_c_api(torch, capi, C, dev, [(128, 784, True), (10, 128, False)], X, 5,
+                                              "quantized_linear_create + quantized_linear_forward per layer (device-resident tensors; "
+                                              "each call allocates its output and synchronises)")
     else:
         name = ("transformer projections: tokens 32768 x d_model 4096, Q/K/V as one GEMM with N = 12288 plus O (N = 4096), "
                 "weights per channel, bias, fp32 out")
@@ -938,6 +1029,9 @@ def secondary_line(torch, D, dev, peaks, a, chk=None):
             D.linear_i8_dequant(xq, wqkv, one(px), sqkv, bqkv, out=qkv)
             D.linear_i8_dequant(xq, ws_[3][0], one(px), ws_[3][1], bs[3], out=o)
         note = "X quantized once per step; Q/K/V in one launch (N = 12288), O in a second; fused per-channel dequant + bias"
+        extra["c_api"] = layers_through_c_api(torch, capi, C, dev, [(Dm, Dm, False)] * 4, X, 3,
+                                              "quantized_linear_forward_shared_input over four layers (device-resident tensors; the call "
+                                              "allocates its outputs and synchronises)", shared=True)
     ms, per_step = timed_replay(torch, D, dev, step, a.steps, a.warmup)
     if a.workload == "c3" and chk is not None:
         # tiles of the fused Q/K/V output and of O against the oracle

@@ -337,6 +337,30 @@ int  rplb_linear_i8_dequant_f32_absmax(const int8_t* x, const int8_t* w, float* 
                                        const float* a_scale, const float* w_scales, const float* bias,
                                        int relu, float* absmax, float* next_scale, void* stream);
 
+/* tensor_quantize_int8 (src/rpl_core.c:521-527, zero point 0) fused into the
+ * layer that consumes it, for layers with few output features: x is the fp32
+ * activation [M,K]; it is quantized with *a_scale on its way into the
+ * contraction (the int8 activation is never written to memory), and the result
+ * is out[m,n] = relu?(((float)acc * *a_scale) * w_scales[n] + bias[n]) as
+ * rplb_linear_i8_dequant_f32 computes it from a quantized copy: same bits.
+ * Such layers are bound by HBM, and this removes a write and a read of the
+ * int8 activation and the buffer that holds it.  absmax / next_scale (both may
+ * be NULL) as in rplb_linear_i8_dequant_f32_absmax.  Shapes: N <= 16 with
+ * K <= 512 and K % 4 == 0 run on dp4a (measured faster than quantize + GEMM:
+ * 14.5 against 18.6 us for 65536 x 128 -> 10); N <= 128 with K <= 896 and
+ * K % 16 == 0 run on the tensor cores with the whole weight matrix resident in
+ * shared memory and converter warps between the TMA loads of fp32 rows and the
+ * MMAs (the conversion is instruction-bound: about as fast as the two kernels
+ * it replaces, 80 against 71 us for 65536 x 784 -> 128; use it to save the
+ * buffer, not the time); anything else is refused with RPLB_E_UNSUPPORTED
+ * (quantize into a buffer instead).
+ * x and w 16-byte aligned.  No counterpart in the reference, which always
+ * materialises the quantized tensor (src/rpl_quantization.c:77-91). */
+int  rplb_quantize_linear_dequant_f32(const float* x, const int8_t* w, float* out,
+                                      uint64_t M, uint64_t K, uint64_t N, uint64_t ldo,
+                                      const float* a_scale, const float* w_scales, const float* bias,
+                                      int relu, float* absmax, float* next_scale, void* stream);
+
 /* Chained quantized layers with a calibrated (static) output scale: the fp32
  * value of rplb_linear_i8_dequant_f32 is quantized in the epilogue exactly as
  * tensor_quantize_int8 would (src/rpl_core.c:523-526) and stored as int8, so
@@ -374,7 +398,9 @@ int  rplb_selftest_bounded_wait_keep(void* stream);
  * 1 = dp4a kernel, 2 = tcgen05 kernel (RPLB_E_UNSUPPORTED if the shape does
  * not fit it), 3 = tcgen05 with one CTA per 128x256 tile, 4 = tcgen05 with a
  * CTA pair (cta_group::2) per 256x256 tile, 5 = tcgen05 with one CTA per
- * 256x256 tile (two accumulators); 2 picks between 3 and 4 by size.
+ * 256x256 tile (two accumulators), 6 = the tcgen05 kernel for few output
+ * features (N <= 128, K <= 896, fp32 epilogue only; the automatic choice for
+ * such layers over many rows); 2 picks between 3, 4 and 6 by shape.
  * Returns the previous setting.  All of them are CUDA kernels. */
 int  rplb_gemm_backend(int which);
 /* How the tensor-core kernels of the calling thread store four-byte outputs:

@@ -18,9 +18,9 @@ LIB_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(LIB_DIR, "obj")
 LIB_PATH = os.path.join(LIB_DIR, "librpl.so")
 
-CU_SOURCES = ["runtime.cu", "quant_kernels.cu", "gemm_i8_simt.cu", "gemm_i8_tcgen05.cu", "gemm_api.cu", "sharded.cu"]
+CU_SOURCES = ["runtime.cu", "quant_kernels.cu", "gemm_i8_simt.cu", "gemm_i8_tcgen05.cu", "gemm_i8_fused_quant.cu", "gemm_api.cu", "sharded.cu"]
 C_SOURCES = ["rpl_host.c"]
-HEADERS = ["common.cuh", "gemm_common.cuh"]
+HEADERS = ["common.cuh", "gemm_common.cuh", "gemm_tc_common.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--default-stream", "legacy"]

@@ -132,6 +132,7 @@ SIGNATURES = {
     "rplb_linear_i8_dequant_f32_arriving": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int,
                                                    _vp, C.c_uint32, C.c_uint32, C.c_uint32, _vp]),
     "rplb_linear_i8_dequant_f32_absmax": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
+    "rplb_quantize_linear_dequant_f32": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _vp, _vp]),
     "rplb_linear_i8_requant_i8": ("rc", [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp, _vp, _vp, C.c_int, _vp, _i, _vp]),
     "rplb_gemm_backend": (C.c_int, [C.c_int]),
     "rplb_gemm_epilogue": (C.c_int, [C.c_int]),

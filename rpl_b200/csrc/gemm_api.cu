@@ -10,11 +10,12 @@ int gemm_tcgen05_status(bool clear);     // gemm_i8_tcgen05.cu
 int bounded_wait_selftest(cudaStream_t st);
 int bounded_wait_leave_status(cudaStream_t st);
 
-// Per host thread: 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA
+// Per host thread: 0 auto, 1 dp4a, 2 tcgen05, 3 tcgen05 128x256 tiles, 4 tcgen05 CTA pair, 5 tcgen05 256x256 tiles per CTA,
+// 6 tcgen05 kernel for few output features
 static thread_local int t_backend = 0;
 int thread_gemm_backend(int which) {
     const int prev = t_backend;
-    if (which >= 0 && which <= 5) t_backend = which;
+    if (which >= 0 && which <= 6) t_backend = which;
     return prev;
 }
 
@@ -111,6 +112,7 @@ int run_gemm(GemmProblem p, cudaStream_t st) {
     // 16-byte multiples; backends 4 and 5 get a transposed, K-contiguous copy instead.
     const bool b_in_place = p.b_is_kn && p.N % 16 == 0 && (((uintptr_t)p.B & 15) == 0) &&
                             (backend == 0 || backend == 2 || backend == 3);
+    if (backend == 6 && (p.b_is_kn || zero_points)) return fail(RPLB_E_UNSUPPORTED, "the kernel for few output features takes W as [N,K] and no zero points");
     if (want_tc && b_in_place && zero_points) {
         // Row sums of A and column sums of B, both taken from the operands as they lie.
         const size_t rs_bytes = ((size_t)p.M * 4 + 255) & ~(size_t)255;
@@ -240,6 +242,33 @@ int rplb_linear_i8_dequant_f32_peers(const int8_t* x, const int8_t* w, float* ou
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "%s: needs K %% 16 == 0 and 16-byte aligned x and w", who);
     return gemm_tcgen05(p, as_stream(stream), 1);
+}
+
+int rplb_quantize_linear_dequant_f32(const float* x, const int8_t* w, float* out, uint64_t M, uint64_t K, uint64_t N,
+                                     uint64_t ldo, const float* a_scale, const float* w_scales, const float* bias,
+                                     int relu, float* absmax, float* next_scale, void* stream) {
+    const char* who = "rplb_quantize_linear_dequant_f32";
+    if (!a_scale || !w_scales) return fail(RPLB_E_BAD_ARG, "%s: null scale pointer", who);
+    if (next_scale && !absmax) return fail(RPLB_E_BAD_ARG, "%s: next_scale needs absmax", who);
+    if (M == 0 || N == 0) return 0;
+    if (!x || !w || !out) return fail(RPLB_E_BAD_ARG, "%s: null pointer", who);
+    if (ldo < N) return fail(RPLB_E_BAD_ARG, "%s: output row stride %llu < N %llu", who, (unsigned long long)ldo, (unsigned long long)N);
+    cudaStream_t st = as_stream(stream);
+    GemmProblem p = {};
+    p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+    p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
+    p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu; p.absmax_out = absmax;
+    const bool small = quantize_linear_small_supports(x, p), tc = gemm_fused_quant_supports(x, p);
+    if (!small && !tc)
+        return fail(RPLB_E_UNSUPPORTED, "%s: needs N <= 128 with K <= 896 and K %% 16 == 0, or N <= 16 with K <= 512 and K %% 4 == 0; "
+                    "quantize into a buffer and call rplb_linear_i8_dequant_f32 instead", who);
+    if (absmax) if (int rc = cuda_ok(cudaMemsetAsync(absmax, 0, sizeof(float), st), "cudaMemsetAsync(absmax)")) return rc;
+    if (int rc = small ? quantize_linear_small(x, p, st) : gemm_fused_quant(x, p, st)) return rc;
+    if (next_scale) {
+        absmax_to_scale_kernel<<<1, 1, 0, st>>>(absmax, next_scale);
+        return launched("absmax_to_scale_kernel");
+    }
+    return 0;
 }
 
 int rplb_linear_i8_dequant_f32_arriving(const int8_t* x, const int8_t* w, float* out, uint64_t M, uint64_t K, uint64_t N,

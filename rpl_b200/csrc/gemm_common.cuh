@@ -104,6 +104,17 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant = 0);
 // Which contraction kernel and which store path this host thread's calls use (rplb_gemm_backend, rplb_gemm_epilogue).
 int thread_gemm_backend(int which);
 int thread_gemm_epilogue(int which);
+// Quantize fused into the contraction's A side: x is fp32 [M,K] and is quantized with *p.a_scale on its way
+// in (p.A is not used).  gemm_fused_quant: tensor cores, N <= 128 and K <= 896; quantize_linear_small: dp4a,
+// N <= 16 and K <= 512.  Both: fp32 epilogue only.
+bool gemm_fused_quant_supports(const float* x, const GemmProblem& p);
+int gemm_fused_quant(const float* x, const GemmProblem& p, cudaStream_t st);
+// The same kernel for an activation that is int8 already: the contraction for few output features (whole weight
+// matrix resident in shared memory, 128-column accumulators, fp32 epilogue only).
+bool gemm_narrow_supports(const GemmProblem& p);
+int gemm_narrow(const GemmProblem& p, cudaStream_t st);
+bool quantize_linear_small_supports(const float* x, const GemmProblem& p);
+int quantize_linear_small(const float* x, const GemmProblem& p, cudaStream_t st);
 // Argument checks and choice of kernel for one contraction (gemm_api.cu).
 int run_gemm(GemmProblem p, cudaStream_t st);
 // True when the tensor-core kernel can take the problem as it stands.

@@ -128,6 +128,103 @@ gemm_i8_simt_kernel(GemmProblem p) {
     if (fp_mode && p.absmax_out) absmax_publish(p.absmax_out, absmax);
 }
 
+// ---------------------------------------------------------------------------
+// Quantize fused into a layer with very few output features (the last layer of
+// the quantized MLP: 128 -> 10): out[m,n] = relu?(((float)acc * sA) * sW[n] + bias[n])
+// with acc = sum_k q(x[m,k]) * w[n,k] and q = tensor_quantize_int8's statement
+// (src/rpl_core.c:523-526) with the scale *a_scale.  The fp32 activation is read
+// once, coalesced (a warp takes 32 rows; lane l loads quad l of each row), quantized
+// in registers and transposed through a 32 x 33-word shared-memory tile, after
+// which lane l owns row l and accumulates its N dot products with dp4a against the
+// weight words held in shared memory (every lane reads the same word: a broadcast).
+// Neither the int8 activation nor a 128- or 256-column tensor-core tile is
+// materialised for a handful of outputs.
+constexpr int SMALL_N_MAX = 16;
+constexpr int SMALL_K_MAX = 512;
+constexpr int SMALL_WARPS = 8;
+
+template <int NT>                      // the number of output features, known at compile time: the inner loop has no tests
+__global__ void __launch_bounds__(SMALL_WARPS * 32, 2)
+quantize_linear_small_kernel(const float* __restrict__ x, const GemmProblem p) {
+    __shared__ uint32_t w_words[SMALL_N_MAX * SMALL_K_MAX / 4];          // [N][K/4]
+    __shared__ uint32_t tiles[SMALL_WARPS][32 * 33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t N = NT;
+    const uint32_t K = (uint32_t)p.K, kw = K / 4;
+    for (uint32_t i = threadIdx.x; i < N * kw; i += blockDim.x) w_words[i] = __ldg(reinterpret_cast<const uint32_t*>(p.B) + i);
+    __syncthreads();
+    const QuantConsts qc = make_quant_consts(__ldg(p.a_scale), 0);
+    const float a_scale = qc.scale;
+    const bool has_bias = p.bias_f32 != nullptr, relu = p.relu != 0;
+    uint32_t* tile = tiles[warp];
+    float absmax = 0.0f;
+    const uint64_t groups = (p.M + 31) / 32;
+    for (uint64_t g = (uint64_t)blockIdx.x * SMALL_WARPS + warp; g < groups; g += (uint64_t)gridDim.x * SMALL_WARPS) {
+        const uint64_t m0 = g * 32;
+        int32_t acc[NT];
+        #pragma unroll
+        for (int n = 0; n < NT; n++) acc[n] = 0;
+        for (uint32_t c0 = 0; c0 < kw; c0 += 32) {                      // 32 words = 128 k per pass
+            const uint32_t j = c0 + lane;                                // this lane's word of every row
+            __syncwarp();                                                // the previous pass has been read out of the tile
+            #pragma unroll 1
+            for (int half = 0; half < 2; half++) {                       // sixteen rows at a time: 16 loads in flight per lane
+                float4 v[16];
+                #pragma unroll
+                for (int r = 0; r < 16; r++) {
+                    const uint64_t m = m0 + half * 16 + r;
+                    v[r] = (j < kw && m < p.M) ? __ldcs(reinterpret_cast<const float4*>(x + m * K) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                #pragma unroll
+                for (int r = 0; r < 16; r++)
+                    tile[(half * 16 + r) * 33 + lane] = (j < kw && m0 + half * 16 + r < p.M) ? quantize_quad_packed(v[r], qc) : 0u;
+            }
+            __syncwarp();
+            const uint32_t words = min(32u, kw - c0);
+            for (uint32_t t = 0; t < words; t++) {
+                const int a = (int)tile[lane * 33 + t];                  // row `lane`, word c0 + t
+                #pragma unroll
+                for (int n = 0; n < NT; n++) acc[n] = __dp4a(a, (int)w_words[n * kw + c0 + t], acc[n]);
+            }
+        }
+        const uint64_t m = m0 + lane;
+        if (m < p.M) {
+            float* row = static_cast<float*>(p.out) + m * p.ldo;
+            #pragma unroll
+            for (int n = 0; n < NT; n++) {
+                const float o = dequant_f32(acc[n], a_scale, __ldg(p.w_scales + n), has_bias, has_bias ? __ldg(p.bias_f32 + n) : 0.0f, relu);
+                if (p.absmax_out) absmax_fold(absmax, o);
+                row[n] = o;
+            }
+        }
+    }
+    if (p.absmax_out) absmax_publish(p.absmax_out, absmax);
+}
+
+bool quantize_linear_small_supports(const float* x, const GemmProblem& p) {
+    return p.mode == EPI_DEQUANT_F32 && !p.b_is_kn && !p.n_peers && !p.a_ready && p.M && p.N && p.K &&
+           p.N <= (uint64_t)SMALL_N_MAX && p.K <= (uint64_t)SMALL_K_MAX && p.K % 4 == 0 &&
+           (((uintptr_t)x & 15) == 0) && (((uintptr_t)p.B & 3) == 0);
+}
+
+int quantize_linear_small(const float* x, const GemmProblem& p, cudaStream_t st) {
+    if (!quantize_linear_small_supports(x, p))
+        return fail(RPLB_E_UNSUPPORTED, "fused quantize + small linear needs N <= %d, K <= %d, K %% 4 == 0, aligned x and w", SMALL_N_MAX, SMALL_K_MAX);
+    const uint64_t groups = (p.M + 31) / 32;
+    uint64_t want = (groups + SMALL_WARPS - 1) / SMALL_WARPS;
+    uint64_t cap = (uint64_t)sm_count() * 4;
+    if (cap == 0) cap = 148 * 4;
+    const unsigned int grid = (unsigned int)(want < cap ? want : cap);
+    switch (p.N) {
+#define RPLB_SMALL_N(NT) case NT: quantize_linear_small_kernel<NT><<<grid, SMALL_WARPS * 32, 0, st>>>(x, p); break;
+        RPLB_SMALL_N(1) RPLB_SMALL_N(2) RPLB_SMALL_N(3) RPLB_SMALL_N(4) RPLB_SMALL_N(5) RPLB_SMALL_N(6) RPLB_SMALL_N(7) RPLB_SMALL_N(8)
+        RPLB_SMALL_N(9) RPLB_SMALL_N(10) RPLB_SMALL_N(11) RPLB_SMALL_N(12) RPLB_SMALL_N(13) RPLB_SMALL_N(14) RPLB_SMALL_N(15) RPLB_SMALL_N(16)
+#undef RPLB_SMALL_N
+        default: return fail(RPLB_E_UNSUPPORTED, "fused quantize + small linear: N = %llu", (unsigned long long)p.N);
+    }
+    return launched("quantize_linear_small_kernel");
+}
+
 int gemm_simt(const GemmProblem& p, cudaStream_t st) {
     if (p.M == 0 || p.N == 0) return 0;
     uint64_t gx = (p.M + BM - 1) / BM, gy = (p.N + BN - 1) / BN;

@@ -910,10 +910,25 @@ Tensor* quantized_linear_forward(QuantizedLinear* layer, const Tensor* input, bo
     const float* x = (const float*)to_device(0, src, M * K * 4);
     float* o = dev_in ? out->data : (float*)stage(3, M * N * 4);
     if ((M * K && !x) || !o) { tensor_free(out); return NULL; }
-    if (report(rplb_quantize_symmetric_f32_i8(x, layer->act, M * K, layer->act_params, NULL), who) != 0 ||
-        report(rplb_linear_i8_dequant_f32(layer->act, layer->weight->data, o, M, K, N, N, &layer->act_params->scale_sym,
-                                          layer->weight->scales, layer->bias, relu ? 1 : 0, NULL), who) != 0 ||
-        (!dev_in && report(rplb_copy(out->data, o, M * N * 4, NULL), who) != 0) || finish(who) != 0) {
+    /* Layers with a handful of output features (N <= 16, K <= 512): the quantize step rides inside the dp4a
+     * contraction and the int8 activation is never written, which is faster than two kernels there.  (For wider
+     * layers the fused tensor-core kernel is no faster than quantize + GEMM, so those keep the two-step route.)
+     * A refusal (alignment) falls back to the two-step route as well.  Same bits either way. */
+    int rc = RPLB_E_UNSUPPORTED;
+    if (N <= 16 && K <= 512 && K % 4 == 0) {
+        rc = report(rplb_minmax_f32(x, M * K, layer->act_params, NULL), who);
+        if (rc == 0)
+            rc = rplb_quantize_linear_dequant_f32(x, layer->weight->data, o, M, K, N, N, &layer->act_params->scale_sym,
+                                                  layer->weight->scales, layer->bias, relu ? 1 : 0, NULL, NULL, NULL);
+        if (rc != 0 && rc != RPLB_E_UNSUPPORTED) report(rc, who);
+    }
+    if (rc == RPLB_E_UNSUPPORTED) {
+        rc = report(rplb_quantize_symmetric_f32_i8(x, layer->act, M * K, layer->act_params, NULL), who);
+        if (rc == 0)
+            rc = report(rplb_linear_i8_dequant_f32(layer->act, layer->weight->data, o, M, K, N, N, &layer->act_params->scale_sym,
+                                                   layer->weight->scales, layer->bias, relu ? 1 : 0, NULL), who);
+    }
+    if (rc != 0 || (!dev_in && report(rplb_copy(out->data, o, M * N * 4, NULL), who) != 0) || finish(who) != 0) {
         tensor_free(out);
         return NULL;
     }

@@ -35,7 +35,8 @@ def launch_count():
 
 
 def gemm_backend(which):
-    """0 automatic, 1 dp4a, 2 tcgen05 (3 = 128x256 tiles, 4 = CTA-pair 256x256 tiles, 5 = 256x256 tiles per CTA);
+    """0 automatic, 1 dp4a, 2 tcgen05 (3 = 128x256 tiles, 4 = CTA-pair 256x256 tiles, 5 = 256x256 tiles per CTA,
+    6 = the kernel for few output features);
     returns the previous setting."""
     return int(capi.load().rplb_gemm_backend(int(which)))
 
@@ -270,6 +271,29 @@ def linear_i8_dequant_absmax(x, w, a_scale, w_scales, bias=None, relu=False, out
     capi.call("rplb_linear_i8_dequant_f32_absmax", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales),
               _p(bias), 1 if relu else 0, _p(stats[0:1]), _p(stats[1:2]), _stream())
     return out, stats[0:1], stats[1:2]
+
+
+def quantize_linear_dequant(x, w, a_scale, w_scales, bias=None, relu=False, out=None, stats=None):
+    """Quantize fused into the layer: ``x`` is fp32 ``[M,K]``, quantized with the device scalar ``a_scale`` on
+    its way into the contraction; otherwise as ``linear_i8_dequant``.  With ``stats`` (a 2-element float32 CUDA
+    tensor) the call also leaves max |out| and max |out| / 127 there.  Few output features only (see
+    ``rplb_quantize_linear_dequant_f32``); other shapes raise ``RplError`` with code ``RPLB_E_UNSUPPORTED``."""
+    _need(x, torch.float32, "x")
+    _need(w, torch.int8, "w")
+    _need(w_scales, torch.float32, "w_scales")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError("w must be [N, K] with K = %d" % K)
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    ldo = out.stride(0) if M > 1 else max(N, out.stride(0))
+    capi.call("rplb_quantize_linear_dequant_f32", _p(x), _p(w), _p(out), M, K, N, ldo, _p(a_scale), _p(w_scales), _p(bias),
+              1 if relu else 0, _p(stats[0:1]) if stats is not None else None, _p(stats[1:2]) if stats is not None else None,
+              _stream())
+    return out
 
 
 def linear_i8_requant_i8(x, w, a_scale, w_scales, out_scale, out_zero_point=0, bias=None, relu=False, out=None):

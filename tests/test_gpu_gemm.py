@@ -9,7 +9,7 @@ from conftest import bits
 
 pytestmark = pytest.mark.gpu
 
-SIMT, TC, TC_SINGLE, TC_PAIR, TC_WIDE = 1, 2, 3, 4, 5      # rplb_gemm_backend codes
+SIMT, TC, TC_SINGLE, TC_PAIR, TC_WIDE, TC_NARROW = 1, 2, 3, 4, 5, 6      # rplb_gemm_backend codes
 
 
 def same(a, b):
@@ -315,3 +315,83 @@ def test_gemm_int8_reads_b_kn_in_place(cuda, lib, port, backend, mnk):
         assert D.launch_count() - before == 1                  # the GEMM alone: no transpose pass
         assert same(got, port.gemm_requant(A, B, 0.013, 0.021, 0.37)), which
     assert same(host(D.gemm_i8_requant(dev(A, cuda), dev(B, cuda))), port.gemm_requant(A, B))
+
+
+# (M, N, K): tensor-core route (N <= 128, K <= 896, K % 16 == 0) and dp4a route (N <= 16, K <= 512, K % 4 == 0)
+FUSED_SHAPES = [(1000, 128, 784), (128, 128, 128), (300, 100, 896), (65, 17, 16), (4096, 64, 400), (257, 128, 880),
+                (1000, 10, 128), (33, 16, 512), (5, 1, 4), (700, 3, 100), (2048, 10, 132)]
+
+
+@pytest.mark.parametrize("mnk", FUSED_SHAPES)
+@pytest.mark.parametrize("relu", [False, True])
+def test_quantize_fused_into_the_layer(cuda, lib, port, backend, mnk, relu):
+    """rplb_quantize_linear_dequant_f32: the int8 activation is never written, the result is the one the
+    two-step path gives (quantize with the given scale, then the contraction with the fused epilogue)."""
+    from rpl_b200 import capi
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    x = (rng.standard_normal((M, K)) * 2.0).astype(np.float32)
+    x[0, :4] = [0.5 * 0.03, 1.5 * 0.03, -2.5 * 0.03, 1e9]            # ties and a value far outside the range
+    wq = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 1e-3).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    sa = np.float32(0.03)
+    xq = port.quantize(x, sa, 0)
+    want = port.linear_dequant(xq, wq, sa, ws, bias, relu)
+    a_dev = dev(np.array([sa], np.float32), cuda)
+    stats = torch.zeros(2, device=cuda)
+    wide = torch.full((M, N + 12), -3.0, device=cuda)                  # a column block of a wider matrix
+    for out in (None, wide[:, 4:4 + N]):
+        got = D.quantize_linear_dequant(dev(x, cuda), dev(wq, cuda), a_dev, dev(ws, cuda), dev(bias, cuda), relu, out=out, stats=stats)
+        torch.cuda.synchronize()
+        assert D.kernel_status(True) == 0
+        assert same(host(got), want)
+        amax = np.float32(np.abs(want).max())
+        assert same(host(stats)[0], amax) and same(host(stats)[1], amax / np.float32(127.0))
+    assert (host(wide[:, :4]) == -3.0).all() and (host(wide[:, 4 + N:]) == -3.0).all()
+    # the same bits as the two-step device path
+    two = D.linear_i8_dequant(D.quantize_dev(dev(x, cuda), a_dev), dev(wq, cuda), a_dev, dev(ws, cuda), dev(bias, cuda), relu)
+    assert same(host(two), want)
+
+
+def test_quantize_fused_refuses_other_shapes(cuda, lib, backend):
+    from rpl_b200 import capi
+    D = backend
+    s = torch.ones(1, device=cuda)
+    for M, N, K in ((64, 129, 128), (64, 128, 912), (64, 64, 24), (64, 17, 516)):
+        with pytest.raises(capi.RplError) as e:
+            D.quantize_linear_dequant(torch.zeros((M, K), device=cuda), torch.zeros((N, K), dtype=torch.int8, device=cuda), s,
+                                      torch.ones(N, device=cuda))
+        assert e.value.code == capi.RPLB_E_UNSUPPORTED
+
+
+@pytest.mark.parametrize("mnk", [(1000, 128, 784), (128, 128, 128), (300, 100, 896), (65, 17, 16), (257, 10, 128),
+                                 (20000, 128, 784), (19000, 10, 128)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_kernel_for_few_output_features(cuda, lib, port, backend, mnk, relu):
+    """The tensor-core kernel with the whole weight matrix resident in shared memory (backend 6, and the automatic
+    choice once every SM gets a tile): same bits as the checker, absmax included."""
+    from rpl_b200 import capi
+    D = backend
+    M, N, K = mnk
+    rng = np.random.default_rng(M + N + K)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng.random(N) + 0.5) * 2e-4).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    a_scale = np.float32(0.0231)
+    want = port.linear_dequant(A, W, a_scale, ws, bias, relu)
+    a_dev = dev(np.array([a_scale], np.float32), cuda)
+    for which in (TC_NARROW, 0):
+        D.gemm_backend(which)
+        got, amax, nxt = D.linear_i8_dequant_absmax(dev(A, cuda), dev(W, cuda), a_dev, dev(ws, cuda), dev(bias, cuda), relu)
+        torch.cuda.synchronize()
+        assert D.kernel_status(True) == 0
+        assert same(host(got), want), which
+        assert same(host(amax)[0], np.float32(np.abs(want).max()))
+    D.gemm_backend(TC_NARROW)
+    with pytest.raises(capi.RplError):                       # other epilogues and wider layers are refused, not emulated
+        D.linear_i8(dev(A, cuda), dev(W, cuda))
+    with pytest.raises(capi.RplError):
+        D.linear_i8_dequant(dev(A[:64], cuda), torch.zeros((256, K), dtype=torch.int8, device=cuda), a_dev, torch.ones(256, device=cuda))
