@@ -56,8 +56,11 @@ def parse_args():
     ap.add_argument("--schedule", default="rows", choices=["rows", "replicated"],
                     help="rows: every rank holds, quantizes and sends only its rows of A (the default at every N); "
                          "replicated: every rank holds and quantizes all of A (comparison only, N > 1)")
+    ap.add_argument("--no-numa", action="store_true", help="allocate the page-locked host buffers wherever the process happens to run "
+                    "(default: on the CPUs next to the rank's GPU)")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
+    ap.add_argument("--sweep-elements", type=int, default=0, help="with --sweep-only: that one tensor size instead of 2^26, 2^20 and 2^30")
     ap.add_argument("--overlap", type=int, default=0,
                     help="replicated schedule only: row blocks for pipelining the quantize pass under the GEMM (0 = sequential)")
     ap.add_argument("--gemm-backend", type=int, default=0, help="rplb_gemm_backend code (0 auto, 3 tcgen05 128x256 tiles, 4 CTA pair, 5 256x256 tiles per CTA)")
@@ -526,6 +529,10 @@ def run_ours(a):
         os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // max(world, 1)))   # torchrun pins it to 1
         chk = Checker()
     if a.sweep_only:
+        if a.sweep_elements:
+            print(json.dumps({"quantize_sweep": quantize_sweep_one(torch, D, dev, peaks, a.sweep_elements, chk),
+                              "parity": chk.result() if chk else None}), flush=True)
+            return
         print(json.dumps({"quantize_sweep": quantize_sweep(torch, D, dev, peaks, chk),
                           "parity": chk.result() if chk else None}), flush=True)
         return
@@ -684,7 +691,10 @@ def run_ours(a):
     if not a.no_e2e and layer is not None:
         xh = oh = None
         try:
-            with NearGpu(torch, dev):
+            near = NearGpu(torch, dev)
+            if a.no_numa:
+                near.cpus = None
+            with near:
                 xh = torch.empty((max(rc, 1), K), dtype=torch.float32, pin_memory=True)
                 oh = torch.empty((M, max(count, 1)), dtype=torch.float32, pin_memory=True)
                 oh.zero_()                                  # touch the pages while the process is near its GPU
@@ -735,7 +745,9 @@ def run_ours(a):
                    "steps": esteps, "h2d_bytes_per_step": int(M * K * 4), "d2h_bytes_per_step": int(M * N * 4),
                    "api": "rplb_sharded_linear_submit_host / rplb_sharded_linear_drain (C ABI, page-locked host buffers; "
                           "every rank uploads its own rows of A and downloads its own output columns)",
-                   "matches_device_run": same, "gpu_launches": int(e2e_launches)}
+                   "matches_device_run": same, "gpu_launches": int(e2e_launches),
+                   "host_buffers": "page-locked, allocated on the CPUs next to the GPU (%d CPUs)" % len(near.cpus) if near.cpus
+                   else "page-locked, no CPU affinity set"}
         del xh, oh
 
     parity = None
