@@ -90,6 +90,36 @@ def test_transformer_projection_32768x4096x4096(cuda, lib, port):
         assert same(host(out[m0:m0 + 128, n0:n0 + 128]), ref)
 
 
+def test_fused_qkv_projection_n12288(cuda, lib, port):
+    """Q, K and V as one contraction with N = 12288 (three 4096 x 4096 weights stacked, biases stacked,
+    src/rpl_attention.c:175-177) over 8192 tokens: every element equals the three separate projections,
+    and sampled tiles equal the checker."""
+    from rpl_b200 import device as D
+    g = torch.Generator(device=cuda)
+    g.manual_seed(0x5EED0031)
+    T, Dm = 8192, 4096
+    X = torch.randn((T, Dm), device=cuda, generator=g)
+    parts = [D.quantize_per_channel(torch.randn((Dm, Dm), device=cuda, generator=g) * 0.02) for _ in range(3)]
+    biases = [torch.randn(Dm, device=cuda, generator=g) * 0.02 for _ in range(3)]
+    wqkv = torch.cat([p[0] for p in parts]).contiguous()
+    sqkv = torch.cat([p[1] for p in parts]).contiguous()
+    bqkv = torch.cat(biases).contiguous()
+    xq, px = D.quantize_symmetric(X)
+    a_scale = px[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1]
+    fused = D.linear_i8_dequant(xq, wqkv, a_scale, sqkv, bqkv)
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0 and fused.shape == (T, 3 * Dm)
+    for i in range(3):
+        one = D.linear_i8_dequant(xq, parts[i][0], a_scale, parts[i][1], biases[i])
+        assert torch.equal(fused[:, i * Dm:(i + 1) * Dm], one), i
+    rng = np.random.default_rng(5)
+    hs, hws, hb = float(host(a_scale)[0]), host(sqkv), host(bqkv)
+    for _ in range(6):
+        m0, n0 = int(rng.integers(0, T - 128)), int(rng.integers(0, 3 * Dm - 128))       # tiles may straddle two weights
+        ref = port.linear_dequant(host(xq[m0:m0 + 128]), host(wqkv[n0:n0 + 128]), hs, hws[n0:n0 + 128], hb[n0:n0 + 128])
+        assert same(host(fused[m0:m0 + 128, n0:n0 + 128]), ref)
+
+
 def test_large_sharded_gemm_slab(cuda, lib, port):
     """K = 8192, weight rows split over 8 'ranks' of 2048 columns each (run one after
     the other on this GPU), 256 rows of A: the assembled output equals the checker's."""

@@ -101,6 +101,12 @@ def test_row_sharded_layer_on_one_rank(cuda, lib, port, mnk):
         assert same(out.cpu().numpy(), want)
     full = layer.gather(out, M)
     assert torch.equal(full, out)
+    # the forward pass in its two halves (what a caller does to put a timing event between them)
+    halves = torch.zeros((M, N), device=cuda)
+    layer.quantize(dev(x, cuda), M)
+    layer.gemm(M, halves)
+    torch.cuda.synchronize()
+    assert torch.equal(halves, out)
     # host buffers through the pipelined entry point, two calls in flight
     xh = torch.from_numpy(x).pin_memory()
     outs = [torch.empty((M, N), dtype=torch.float32).pin_memory() for _ in range(3)]
