@@ -58,6 +58,8 @@ def parse_args():
                          "replicated: every rank holds and quantizes all of A (comparison only, N > 1)")
     ap.add_argument("--no-numa", action="store_true", help="allocate the page-locked host buffers wherever the process happens to run "
                     "(default: on the CPUs next to the rank's GPU)")
+    ap.add_argument("--no-balance", action="store_true", help="N > 1: keep the even column split instead of re-splitting the columns "
+                    "in proportion to each GPU's GEMM speed measured during warm-up")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
     ap.add_argument("--sweep-elements", type=int, default=0, help="with --sweep-only: that one tensor size instead of 2^26, 2^20 and 2^30")
@@ -544,42 +546,105 @@ def run_ours(a):
 
     replicated = a.schedule == "replicated" and world > 1
     # ---- synthetic inputs: this rank's rows of A (all of A under the replicated schedule), its rows of W ----
-    begin, count = shard_range(N, world, rank, 256)
     r0, rc = (0, M) if replicated else shard_range(M, world, rank, 128)
     A_local = rows_of_a(torch, dev, M, K, r0, rc)
-    g = torch.Generator(device=dev)
-    wq = torch.empty((count, K), dtype=torch.int8, device=dev)
-    wsc = torch.empty(count, dtype=torch.float32, device=dev)
-    blk = 4096
-    for c0 in range(0, count, blk):
-        c1 = min(count, c0 + blk)
-        g.manual_seed(0x5EED0051 + (begin + c0))
-        w = torch.randn((c1 - c0, K), device=dev, generator=g) * 0.02
-        q, s, _ = D.quantize_per_channel(w)
-        wq[c0:c1] = q
-        wsc[c0:c1] = s
-    del w, q, s
-    out = torch.empty((M, count), dtype=torch.float32, device=dev)
     ops_total = 2.0 * M * N * K
+
+    def weight_rows(begin, count):
+        """Rows [begin, begin + count) of the synthetic weight ~ N(0, 0.02), quantized per output channel: generated
+        in units of 256 rows, each from its own seed, so that every split of the columns yields the same matrix."""
+        g = torch.Generator(device=dev)
+        wq = torch.empty((count, K), dtype=torch.int8, device=dev)
+        wsc = torch.empty(count, dtype=torch.float32, device=dev)
+        u = begin // 256
+        while u * 256 < begin + count:
+            g.manual_seed(0x5EED0051 + 104729 * u)
+            w = torch.randn((min(256, N - u * 256), K), device=dev, generator=g) * 0.02
+            q, sc, _ = D.quantize_per_channel(w)
+            lo, hi = max(begin, u * 256), min(begin + count, (u + 1) * 256)
+            wq[lo - begin:hi - begin] = q[lo - u * 256:hi - u * 256]
+            wsc[lo - begin:hi - begin] = sc[lo - u * 256:hi - u * 256]
+            u += 1
+        return wq, wsc
+
+    class State:
+        pass
+    st = State()
+
+    def build(column_counts):
+        """This rank's weights, output block and layer for a split of the columns (None = even)."""
+        if column_counts is None:
+            st.begin, st.count = shard_range(N, world, rank, 256)
+        else:
+            st.begin, st.count = sum(column_counts[:rank]), column_counts[rank]
+        st.wq, st.wsc = weight_rows(st.begin, st.count)
+        st.out = torch.empty((M, st.count), dtype=torch.float32, device=dev)
+        if replicated:
+            st.old = ShardedQuantizedLinear(st.wq, st.wsc, None, n_total=N, rank=rank, world=world)
+            st.layer = None
+        else:
+            st.layer = RowShardedLinear(st.wq, st.wsc, None, n_total=N, max_rows=M, rank=rank, world=world, column_counts=column_counts)
+
+    build(None)
+
+    def quantize_half():
+        if replicated:
+            st.old.quantize_activation(A_local)
+        else:
+            st.layer.quantize(A_local, M)
+
+    def gemm_half():
+        if replicated:
+            st.old.gemm(st.old._xq, st.old._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], out=st.out)
+        else:
+            st.layer.gemm(M, st.out)
+
+    # ---- N > 1: the GPUs of a node do not sustain the same clock under their power cap, and a step ends when the
+    # slowest rank does.  Measure every rank's GEMM under sustained load and deal the columns out in proportion to speed. ----
+    balance = None
+    if world > 1 and not replicated and not a.no_balance:
+        from rpl_b200.sharded import weighted_column_counts
+        # About a second of steps first: what counts is the clock each GPU settles at under its power cap, and a
+        # cold GPU runs faster than that.  Every rank runs the same number of steps (a step contains a collective).
+        t_pre = time.time()
+        for _ in range(3):
+            quantize_half()
+            gemm_half()
+        torch.cuda.synchronize()
+        n_pre = torch.tensor([max(1, min(2000, int(1.0 / max((time.time() - t_pre) / 3, 1e-4))))], device=dev)
+        dist.broadcast(n_pre, src=0)
+        for _ in range(int(n_pre.item())):
+            quantize_half()
+            gemm_half()
+        pairs = []
+        for _ in range(8):
+            quantize_half()
+            e_a, e_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e_a.record()
+            gemm_half()
+            e_b.record()
+            pairs.append((e_a, e_b))
+        torch.cuda.synchronize()
+        mine = torch.tensor([sum(event_ms(pairs)) / len(pairs)], device=dev, dtype=torch.float64)
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        times = [float(t.item()) for t in every]
+        counts = weighted_column_counts(N, [1.0 / t for t in times])
+        even = [shard_range(N, world, r, 256)[1] for r in range(world)]
+        # Run-to-run noise of a GPU's GEMM time is about 2 %: re-split only for a spread well above that.
+        spread = max(times) / min(times)
+        if spread < 1.04:
+            counts = even
+        balance = {"gemm_ms_even_split": [round(t, 4) for t in times], "spread": round(spread, 4), "threshold": 1.04,
+                   "columns_even_split": even, "columns": counts}
+        if counts != even and min(counts) > 0:
+            dist.barrier()
+            st.layer.close()
+            del st.out, st.wq, st.wsc
+            torch.cuda.empty_cache()
+            build(counts)
+    count, out, wq, wsc, layer = st.count, st.out, st.wq, st.wsc, st.layer
     ops_rank = 2.0 * M * count * K
-
-    if replicated:
-        old = ShardedQuantizedLinear(wq, wsc, None, n_total=N, rank=rank, world=world)
-        layer = None
-
-        def quantize_half():
-            old.quantize_activation(A_local)
-
-        def gemm_half():
-            old.gemm(old._xq, old._params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1], out=out)
-    else:
-        layer = RowShardedLinear(wq, wsc, None, n_total=N, max_rows=M, rank=rank, world=world)
-
-        def quantize_half():
-            layer.quantize(A_local, M)
-
-        def gemm_half():
-            layer.gemm(M, out)
 
     def step_fn():
         quantize_half()
@@ -785,6 +850,8 @@ def run_ours(a):
         "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": workload_name(a), "parallelism": "output columns and activation rows split over %d rank(s), output left column-sharded" % world,
                    "columns_per_rank": count, "rows_per_rank": rc, "schedule": sched,
+                   "column_split": ("in proportion to each rank's GEMM speed measured under sustained load before the timed region" if balance and balance["columns"] != balance["columns_even_split"]
+                                    else "even"),
                    "l2": "no flush: per-step inputs and outputs exceed L2 (A rows %.2f GiB fp32, int8 A %.2f GiB, out %.1f GiB per rank)"
                    % (rc * K * 4 / 2**30, M * K / 2**30, M * count * 4 / 2**30)},
         "breakdown_ms": {"quantize_A_and_scale_agreement": quant_ms, "gemm_with_epilogue": gemm_ms,
@@ -798,9 +865,12 @@ def run_ours(a):
                      "ms_x_mhz": gemm_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "parity": parity,
     }
+    if balance is not None:
+        line["balance"] = balance
     if gather is not None:
         line["gather"] = gather
     del A_local, out
+    st.out = st.layer = None
     torch.cuda.empty_cache()
     if world == 1 and not a.no_sweep:
         line["quantize_sweep"] = quantize_sweep(torch, D, dev, peaks, chk)
@@ -808,6 +878,7 @@ def run_ours(a):
             line["parity"].update(chk.result())
     if world == 1 and not a.no_secondary:
         del wq, wsc
+        st.wq = st.wsc = None
         torch.cuda.empty_cache()
         line["secondary"] = {}
         for wl in ("c1", "c2", "c3"):

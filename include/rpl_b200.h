@@ -446,6 +446,17 @@ int  rplb_nccl_unique_id(void* id);
 int  rplb_sharded_linear_create(rplb_sharded_linear** layer, int rank, int world, const void* nccl_id, void* nccl_comm,
                                 uint64_t max_rows, uint64_t in_features, uint64_t out_features_total,
                                 const int8_t* weight_rows, const float* scales, const float* bias);
+/* The same with the column blocks chosen by the caller: column_counts[r] columns for rank r, contiguous in
+ * rank order, each a multiple of 256 (the last non-empty one may be ragged), adding up to out_features_total;
+ * NULL = the even split.  The GPUs of a node do not sustain the same clock under their power cap; a split in
+ * proportion to each GPU's measured speed lets all ranks finish together (rplb_shard_weighted computes one:
+ * weights[r] = relative speed of rank r, e.g. 1 / its measured GEMM time; every rank must pass the same
+ * numbers).  weight_rows / scales / bias are the rows of this rank's block under that split. */
+int  rplb_sharded_linear_create_split(rplb_sharded_linear** layer, int rank, int world, const void* nccl_id, void* nccl_comm,
+                                      uint64_t max_rows, uint64_t in_features, uint64_t out_features_total,
+                                      const uint64_t* column_counts, const int8_t* weight_rows, const float* scales,
+                                      const float* bias);
+int  rplb_shard_weighted(uint64_t n, int world, uint64_t align, const double* weights, uint64_t* counts);
 void rplb_sharded_linear_free(rplb_sharded_linear* layer);
 int  rplb_sharded_linear_columns(const rplb_sharded_linear* layer, uint64_t* begin, uint64_t* count);
 int  rplb_sharded_linear_rows(const rplb_sharded_linear* layer, uint64_t rows, uint64_t* begin, uint64_t* count);

@@ -139,6 +139,8 @@ SIGNATURES = {
     "rplb_selftest_bounded_wait_keep": ("rc", [_vp]),
     "rplb_nccl_unique_id": ("rc", [_vp]),
     "rplb_sharded_linear_create": ("rc", [C.POINTER(_vp), C.c_int, C.c_int, _vp, _vp, _u64, _u64, _u64, _vp, _vp, _vp]),
+    "rplb_sharded_linear_create_split": ("rc", [C.POINTER(_vp), C.c_int, C.c_int, _vp, _vp, _u64, _u64, _u64, C.POINTER(_u64), _vp, _vp, _vp]),
+    "rplb_shard_weighted": ("rc", [_u64, C.c_int, _u64, C.POINTER(C.c_double), C.POINTER(_u64)]),
     "rplb_sharded_linear_free": (None, [_vp]),
     "rplb_sharded_linear_columns": ("rc", [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "rplb_sharded_linear_rows": ("rc", [_vp, _u64, C.POINTER(_u64), C.POINTER(_u64)]),

@@ -100,18 +100,19 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t value, uint32_t n) {
     if (i < n) dst[i] = value;
 }
 
+// Where each rank's column block begins (entry `world` = the total): passed to kernels by value.
+struct ColumnSplit {
+    uint64_t begin[9];
+};
+
 // landing[r][m][0..cmax) -> full[m][begin_r .. begin_r + count_r), one element per thread and step.
 __global__ void unpack_columns_kernel(const float* __restrict__ landing, float* __restrict__ full, uint64_t M, uint64_t n_total,
-                                      uint64_t cmax, int world, uint64_t align) {
-    const uint64_t units = (n_total + align - 1) / align;
-    const uint64_t base = units / (uint64_t)world, extra = units % (uint64_t)world;
+                                      uint64_t cmax, int world, ColumnSplit split) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * n_total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t m = i / n_total, n = i % n_total;
-        // owner of column n under the split of rplb_shard_range
-        const uint64_t u = n / align;
-        uint64_t r = (u < extra * (base + 1)) ? u / (base + 1) : extra + (base ? (u - extra * (base + 1)) / base : 0);
-        const uint64_t u0 = r * base + (r < extra ? r : extra);
-        full[i] = landing[(r * M + m) * cmax + (n - u0 * align)];
+        int r = 0;
+        while (r + 1 < world && n >= split.begin[r + 1]) r++;           // owner of column n
+        full[i] = landing[((uint64_t)r * M + m) * cmax + (n - split.begin[r])];
     }
 }
 
@@ -131,6 +132,7 @@ constexpr int kMaxBlocks = 16;       // row blocks of one host-buffer call
 struct ShardedLinear {
     int rank = 0, world = 1;
     uint64_t max_rows = 0, K = 0, n_total = 0, col_begin = 0, col_count = 0;
+    ColumnSplit split = {};              // every rank's first column; split.begin[world] = n_total
     const int8_t* w = nullptr;
     const float* w_scales = nullptr;
     const float* bias = nullptr;
@@ -208,7 +210,8 @@ static int stream_fence(ShardedLinear* h, cudaStream_t st) {
 }
 
 static int create(ShardedLinear** out, int rank, int world, const void* nccl_id, void* nccl_comm, uint64_t max_rows,
-                  uint64_t K, uint64_t n_total, const int8_t* w, const float* w_scales, const float* bias) {
+                  uint64_t K, uint64_t n_total, const uint64_t* column_counts, const int8_t* w, const float* w_scales,
+                  const float* bias) {
     *out = nullptr;
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
         return fail(RPLB_E_BAD_ARG, "sharded linear: rank %d of %d (at most %d ranks)", rank, world, kMaxWorld);
@@ -223,7 +226,25 @@ static int create(ShardedLinear** out, int rank, int world, const void* nccl_id,
     ShardedLinear* h = new ShardedLinear();
     h->rank = rank; h->world = world; h->max_rows = max_rows; h->K = K; h->n_total = n_total;
     h->w = w; h->w_scales = w_scales; h->bias = bias;
-    rplb_shard_range(n_total, world, rank, 256, &h->col_begin, &h->col_count);
+    // The column blocks: dealt evenly, or as the caller says (e.g. in proportion to each GPU's measured speed).
+    uint64_t at = 0;
+    for (int r = 0; r < world; r++) {
+        uint64_t b = 0, c = 0;
+        if (column_counts) { b = at; c = column_counts[r]; }
+        else rplb_shard_range(n_total, world, r, 256, &b, &c);
+        if (b != at || (c % 256 != 0 && at + c != n_total) || at + c > n_total) {
+            delete h;
+            return fail(RPLB_E_BAD_ARG, "sharded linear: column blocks must be contiguous multiples of 256 (the last may be ragged) that add up to %llu",
+                        (unsigned long long)n_total);
+        }
+        h->split.begin[r] = b;
+        at += c;
+    }
+    if (at != n_total) { delete h; return fail(RPLB_E_BAD_ARG, "sharded linear: the column blocks cover %llu of %llu columns",
+                                               (unsigned long long)at, (unsigned long long)n_total); }
+    h->split.begin[world] = n_total;
+    h->col_begin = h->split.begin[rank];
+    h->col_count = h->split.begin[rank + 1] - h->split.begin[rank];
     if (h->col_count && (!w || !w_scales)) { delete h; return fail(RPLB_E_BAD_ARG, "sharded linear: null weight or scale pointer"); }
     const uint64_t max_tiles = (max_rows + 127) / 128;
     h->words_bytes = (size_t)((max_tiles * 4 + 4095) & ~(uint64_t)4095);
@@ -404,14 +425,58 @@ int rplb_nccl_unique_id(void* id) {
     return 0;
 }
 
+int rplb_sharded_linear_create_split(rplb_sharded_linear** layer, int rank, int world, const void* nccl_id, void* nccl_comm,
+                                     uint64_t max_rows, uint64_t in_features, uint64_t out_features_total,
+                                     const uint64_t* column_counts, const int8_t* weight_rows, const float* scales,
+                                     const float* bias) {
+    if (!layer) return fail(RPLB_E_BAD_ARG, "rplb_sharded_linear_create: null result pointer");
+    ShardedLinear* h = nullptr;
+    const int rc = create(&h, rank, world, nccl_id, nccl_comm, max_rows, in_features, out_features_total, column_counts,
+                          weight_rows, scales, bias);
+    *layer = reinterpret_cast<rplb_sharded_linear*>(h);
+    return rc;
+}
+
 int rplb_sharded_linear_create(rplb_sharded_linear** layer, int rank, int world, const void* nccl_id, void* nccl_comm,
                                uint64_t max_rows, uint64_t in_features, uint64_t out_features_total,
                                const int8_t* weight_rows, const float* scales, const float* bias) {
-    if (!layer) return fail(RPLB_E_BAD_ARG, "rplb_sharded_linear_create: null result pointer");
-    ShardedLinear* h = nullptr;
-    const int rc = create(&h, rank, world, nccl_id, nccl_comm, max_rows, in_features, out_features_total, weight_rows, scales, bias);
-    *layer = reinterpret_cast<rplb_sharded_linear*>(h);
-    return rc;
+    return rplb_sharded_linear_create_split(layer, rank, world, nccl_id, nccl_comm, max_rows, in_features, out_features_total,
+                                            nullptr, weight_rows, scales, bias);
+}
+
+int rplb_shard_weighted(uint64_t n, int world, uint64_t align, const double* weights, uint64_t* counts) {
+    if (world <= 0 || world > kMaxWorld || !weights || !counts) return fail(RPLB_E_BAD_ARG, "rplb_shard_weighted: bad arguments");
+    if (align == 0) align = 1;
+    double total = 0.0;
+    for (int r = 0; r < world; r++) {
+        if (!(weights[r] > 0.0) || weights[r] > 1e300) return fail(RPLB_E_BAD_ARG, "rplb_shard_weighted: weight %d is not a positive number", r);
+        total += weights[r];
+    }
+    // Whole units of `align` columns by largest remainder; ties go to the lower rank.  The last unit may be ragged.
+    const uint64_t units = (n + align - 1) / align;
+    uint64_t given = 0, share[kMaxWorld];
+    double rest[kMaxWorld];
+    for (int r = 0; r < world; r++) {
+        const double exact = (double)units * (weights[r] / total);
+        share[r] = (uint64_t)exact;
+        rest[r] = exact - (double)share[r];
+        given += share[r];
+    }
+    while (given < units) {
+        int best = 0;
+        for (int r = 1; r < world; r++) if (rest[r] > rest[best]) best = r;
+        share[best]++;
+        rest[best] = -1.0;
+        given++;
+    }
+    uint64_t at = 0;
+    for (int r = 0; r < world; r++) {
+        uint64_t e = at + share[r] * align;
+        if (e > n) e = n;
+        counts[r] = e - at;
+        at = e;
+    }
+    return 0;
 }
 
 void rplb_sharded_linear_free(rplb_sharded_linear* layer) { destroy(reinterpret_cast<ShardedLinear*>(layer)); }
@@ -470,8 +535,8 @@ int rplb_sharded_linear_gather(rplb_sharded_linear* layer, const float* block, u
         return cuda_ok(cudaMemcpy2DAsync(full, h->n_total * 4, block, ld * 4, h->col_count * 4, rows, cudaMemcpyDeviceToDevice, st),
                        "cudaMemcpy2DAsync(gather)");
     }
-    uint64_t b0, cmax;
-    rplb_shard_range(h->n_total, h->world, 0, 256, &b0, &cmax);          // rank 0 owns the widest block
+    uint64_t cmax = 0;                                                   // the widest block
+    for (int r = 0; r < h->world; r++) cmax = cmax > h->split.begin[r + 1] - h->split.begin[r] ? cmax : h->split.begin[r + 1] - h->split.begin[r];
     const size_t per_rank = (size_t)rows * cmax * 4;
     const size_t want = per_rank * (size_t)h->world;
     if (h->landing_bytes < want) {
@@ -488,7 +553,7 @@ int rplb_sharded_linear_gather(rplb_sharded_linear* layer, const float* block, u
     pack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(block, ld, mine, rows, h->col_count, cmax);
     if (int e = launched("pack_columns_kernel")) return e;
     if (int e = nccl_ok(nccl_api()->AllGather(mine, h->landing, per_rank, kNcclInt8, h->comm, st), "ncclAllGather(columns)")) return e;
-    unpack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(h->landing, full, rows, h->n_total, cmax, h->world, 256);
+    unpack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(h->landing, full, rows, h->n_total, cmax, h->world, h->split);
     return launched("unpack_columns_kernel");
 }
 

@@ -444,6 +444,19 @@ class HostPipeline:
         torch.cuda.current_stream(self.din[0].device).synchronize()
 
 
+def weighted_column_counts(n_total, speeds, align=256):
+    """Column counts per rank in proportion to ``speeds`` (``rplb_shard_weighted``): multiples of ``align``
+    by largest remainder.  Every rank must call it with the same numbers."""
+    import ctypes as C
+
+    from . import capi
+    world = len(speeds)
+    w = (C.c_double * world)(*[float(v) for v in speeds])
+    counts = (C.c_uint64 * world)()
+    capi.call("rplb_shard_weighted", int(n_total), world, int(align), w, counts)
+    return [int(c) for c in counts]
+
+
 class RowShardedLinear:
     """Binding of ``rplb_sharded_linear_*``: the quantized Linear with output columns AND
     activation rows split over the ranks, run entirely by ``librpl.so`` (its own NCCL
@@ -454,7 +467,7 @@ class RowShardedLinear:
     tells which), already in device memory.
     """
 
-    def __init__(self, wq, w_scales, bias, n_total, max_rows, rank=0, world=1, group=None):
+    def __init__(self, wq, w_scales, bias, n_total, max_rows, rank=0, world=1, group=None, column_counts=None):
         import ctypes as C
 
         from . import capi
@@ -471,8 +484,9 @@ class RowShardedLinear:
             dist.broadcast_object_list(box, src=0, group=group)
             ident = (C.c_char * capi.RPLB_NCCL_ID_BYTES).from_buffer_copy(box[0])
         self.handle = C.c_void_p()
-        capi.call("rplb_sharded_linear_create", C.byref(self.handle), rank, world, ident, None, self.max_rows, self.K,
-                  self.n_total, C.c_void_p(wq.data_ptr()), C.c_void_p(w_scales.data_ptr()),
+        counts = (C.c_uint64 * world)(*[int(c) for c in column_counts]) if column_counts is not None else None
+        capi.call("rplb_sharded_linear_create_split", C.byref(self.handle), rank, world, ident, None, self.max_rows, self.K,
+                  self.n_total, counts, C.c_void_p(wq.data_ptr()), C.c_void_p(w_scales.data_ptr()),
                   C.c_void_p(bias.data_ptr()) if bias is not None else None)
         b, c = C.c_uint64(), C.c_uint64()
         capi.call("rplb_sharded_linear_columns", self.handle, C.byref(b), C.byref(c))

@@ -124,3 +124,26 @@ def test_no_cpu_fallback_without_a_device(lib):
     lib.tensor_free(t)
     with pytest.raises(capi.RplError):
         capi.call("rplb_stream_sync", None)
+
+
+@pytest.mark.parametrize("n,weights", [(65536, [1.0] * 8), (65536, [1 / 3.26, 1 / 3.85, 1 / 3.4, 1 / 3.5, 1 / 3.85, 1 / 3.3, 1 / 3.6, 1 / 3.45]),
+                                       (700, [1, 2]), (200, [1, 5]), (1000, [3, 1, 1]), (12288, [1, 1.1, 0.9, 1])])
+def test_weighted_shard_covers_the_columns_in_units_of_256(lib, n, weights):
+    world = len(weights)
+    w = (C.c_double * world)(*weights)
+    counts = (C.c_uint64 * world)()
+    assert lib.rplb_shard_weighted(n, world, 256, w, counts) == 0
+    got = [int(c) for c in counts]
+    assert sum(got) == n
+    at = 0
+    for c in got:
+        if c and at + c < n:
+            assert c % 256 == 0                               # only the block that ends the matrix may be ragged
+        at += c
+    units = (n + 255) // 256
+    for c, wt in zip(got, weights):                           # within one unit of the exact proportional share
+        assert abs((c + 255) // 256 - units * wt / sum(weights)) <= 1.0 + 1e-9
+    if len(set(weights)) == 1:
+        from rpl_b200.sharded import shard_range
+        assert got == [shard_range(n, world, r, 256)[1] for r in range(world)]
+    assert lib.rplb_shard_weighted(n, world, 256, (C.c_double * world)(*([0.0] * world)), counts) != 0

@@ -181,6 +181,27 @@ def _rank_main(rank, world, port_no, result_dir):
                 assert np.array_equal(o.numpy().view(np.uint32), want.view(np.uint32)), "host path, rank %d, M %d" % (rank, M)
         dist.barrier()
         layer.close()
+        # an uneven column split (in proportion to 1, 2, 3 ...: what a caller does for GPUs of unequal speed)
+        from rpl_b200.sharded import weighted_column_counts
+        counts = weighted_column_counts(n_total, [1.0 + r for r in range(world)])
+        b, c = sum(counts[:rank]), counts[rank]
+        wq, ws, _ = D.quantize_per_channel(torch.from_numpy(W[b:b + c]).to(dev_))
+        layer = RowShardedLinear(wq, ws, torch.from_numpy(bias[b:b + c]).to(dev_), n_total=n_total, max_rows=max_rows,
+                                 rank=rank, world=world, column_counts=counts)
+        assert (layer.col_begin, layer.col_count) == (b, c)
+        M = 900
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        r0, rc = layer.rows(M)
+        out = layer.forward(torch.from_numpy(x[r0:r0 + rc]).to(dev_), M)
+        full = layer.gather(out, M)
+        torch.cuda.synchronize()
+        hq, hs = cpu.quantize_symmetric(x)
+        want_full = cpu.linear_dequant(hq, hwq, hs, hws, bias, relu=False)
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want_full[:, b:b + c].view(np.uint32)), "uneven split, rank %d" % rank
+        assert np.array_equal(full.cpu().numpy().view(np.uint32), want_full.view(np.uint32)), "gather with an uneven split, rank %d" % rank
+        assert D.kernel_status(True) == 0
+        dist.barrier()
+        layer.close()
         with open(os.path.join(result_dir, "ok%d" % rank), "w") as f:
             f.write("ok")
     finally:
