@@ -60,6 +60,8 @@ def parse_args():
                     "(default: on the CPUs next to the rank's GPU)")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep the even column split instead of re-splitting the columns "
                     "in proportion to each GPU's GEMM speed measured during warm-up")
+    ap.add_argument("--balance-threshold", type=float, default=1.04,
+                    help="N > 1: re-split the columns only when the slowest rank's GEMM takes this many times the fastest's")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
     ap.add_argument("--sweep-elements", type=int, default=0, help="with --sweep-only: that one tensor size instead of 2^26, 2^20 and 2^30")
@@ -633,9 +635,9 @@ def run_ours(a):
         even = [shard_range(N, world, r, 256)[1] for r in range(world)]
         # Run-to-run noise of a GPU's GEMM time is about 2 %: re-split only for a spread well above that.
         spread = max(times) / min(times)
-        if spread < 1.04:
+        if spread < a.balance_threshold:
             counts = even
-        balance = {"gemm_ms_even_split": [round(t, 4) for t in times], "spread": round(spread, 4), "threshold": 1.04,
+        balance = {"gemm_ms_even_split": [round(t, 4) for t in times], "spread": round(spread, 4), "threshold": a.balance_threshold,
                    "columns_even_split": even, "columns": counts}
         if counts != even and min(counts) > 0:
             dist.barrier()

@@ -377,7 +377,8 @@ int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
 
 /* Status word of the tensor-core kernels launched by the calling host thread:
  * 0, or the code of the bounded wait that expired (1 stage-free, 2 stage-loaded,
- * 3 accumulator-free, 4 accumulator-ready, 5 rows from another GPU).  Every
+ * 3 accumulator-free, 4 accumulator-ready, 5 rows from another GPU; 6 = a bulk
+ * copy of the per-channel quantizer's staged rows did not complete).  Every
  * host thread has a word of its own, so a give-up is seen by the thread that
  * launched the kernel (and refuses that thread's next GEMM until cleared).
  * Readable at any time; clear != 0 resets it.  A kernel that gave up leaves

@@ -14,6 +14,8 @@
 
 namespace rplb {
 
+int* kernel_status_word_device();   // gemm_i8_tcgen05.cu: the calling host thread's status word, as the device sees it
+
 constexpr int kThreads = 256;       // threads per CTA in the streaming kernels
 constexpr int kUnroll = 4;          // quads per thread per grid-stride step
 constexpr int kCtasPerSm = 8;       // 2048 resident threads per SM
@@ -365,7 +367,7 @@ per_channel_staged_kernel(const float* __restrict__ x, int8_t* __restrict__ q, f
         }
         block_minmax(lo, hi, s_lo, s_hi);                 // contains the barrier that also publishes s_abort
         if (s_abort) {
-            if (threadIdx.x == 0) atomicExch(gave_up, 1);
+            if (threadIdx.x == 0) atomicCAS(gave_up, 0, 6);       // status code 6: a bulk copy of a channel did not complete
             return;
         }
         const float scale = channel_scale(lo, hi);
@@ -634,11 +636,12 @@ int rplb_quantize_per_channel_f32_i8(const float* x, int8_t* q, float* scales, i
         if (per < 1) per = 1;
         uint64_t cap2 = (uint64_t)sm_count() * per;
         if (cap2 == 0) cap2 = 148 * per;
-        Scratch sc;
-        if (int rc = scratch_for(st, 256, &sc)) return rc;
+        // A wait that runs out is reported through the calling thread's kernel status word (rplb_kernel_status).
+        int* status_dev = kernel_status_word_device();
+        if (!status_dev) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
         const unsigned int g2 = (unsigned int)(num_channels < cap2 ? num_channels : cap2);
         per_channel_staged_kernel<<<g2, kThreads, tail_bytes, st>>>(x, q, scales, zero_points, num_channels, (uint32_t)row_quads,
-                                                                    reinterpret_cast<int*>(sc.control + 8));
+                                                                    status_dev);
         return launched("per_channel_staged_kernel");
     }
     per_channel_stream_kernel<<<grid, kThreads, 0, st>>>(x, q, scales, zero_points, num_channels, channel_size, vec ? 1 : 0);

@@ -105,14 +105,20 @@ struct ColumnSplit {
     uint64_t begin[9];
 };
 
-// landing[r][m][0..cmax) -> full[m][begin_r .. begin_r + count_r), one element per thread and step.
+// landing[r][m][0..cmax) -> full[m][begin_r .. begin_r + count_r).  VEC = 4: four columns (16 bytes) per thread
+// and step, for splits and widths that are multiples of four columns and 16-byte aligned buffers; VEC = 1 otherwise.
+template <int VEC>
 __global__ void unpack_columns_kernel(const float* __restrict__ landing, float* __restrict__ full, uint64_t M, uint64_t n_total,
                                       uint64_t cmax, int world, ColumnSplit split) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * n_total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t m = i / n_total, n = i % n_total;
+    const uint64_t per_row = n_total / VEC;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * per_row; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t m = i / per_row, n = (i % per_row) * VEC;
         int r = 0;
         while (r + 1 < world && n >= split.begin[r + 1]) r++;           // owner of column n
-        full[i] = landing[((uint64_t)r * M + m) * cmax + (n - split.begin[r])];
+        const float* src = landing + ((uint64_t)r * M + m) * cmax + (n - split.begin[r]);
+        float* dst = full + m * n_total + n;
+        if (VEC == 4) *reinterpret_cast<float4*>(dst) = __ldcs(reinterpret_cast<const float4*>(src));
+        else *dst = *src;
     }
 }
 
@@ -549,11 +555,19 @@ int rplb_sharded_linear_gather(rplb_sharded_linear* layer, const float* block, u
         h->landing = static_cast<float*>(p);
         h->landing_bytes = want;
     }
-    float* mine = h->landing + (size_t)h->rank * rows * cmax;
-    pack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(block, ld, mine, rows, h->col_count, cmax);
-    if (int e = launched("pack_columns_kernel")) return e;
-    if (int e = nccl_ok(nccl_api()->AllGather(mine, h->landing, per_rank, kNcclInt8, h->comm, st), "ncclAllGather(columns)")) return e;
-    unpack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(h->landing, full, rows, h->n_total, cmax, h->world, h->split);
+    // A block that is as wide as the widest and dense is sent as it lies; others are padded into the landing buffer first.
+    const float* send = block;
+    if (h->col_count != cmax || ld != cmax) {
+        float* mine = h->landing + (size_t)h->rank * rows * cmax;
+        pack_columns_kernel<<<(unsigned int)sm_count() * 8, 256, 0, st>>>(block, ld, mine, rows, h->col_count, cmax);
+        if (int e = launched("pack_columns_kernel")) return e;
+        send = mine;
+    }
+    if (int e = nccl_ok(nccl_api()->AllGather(send, h->landing, per_rank, kNcclInt8, h->comm, st), "ncclAllGather(columns)")) return e;
+    bool vec = h->n_total % 4 == 0 && cmax % 4 == 0 && (((uintptr_t)full | (uintptr_t)h->landing) & 15) == 0;
+    for (int r = 0; r < h->world; r++) vec = vec && h->split.begin[r] % 4 == 0;
+    if (vec) unpack_columns_kernel<4><<<(unsigned int)sm_count() * 8, 256, 0, st>>>(h->landing, full, rows, h->n_total, cmax, h->world, h->split);
+    else unpack_columns_kernel<1><<<(unsigned int)sm_count() * 8, 256, 0, st>>>(h->landing, full, rows, h->n_total, cmax, h->world, h->split);
     return launched("unpack_columns_kernel");
 }
 
