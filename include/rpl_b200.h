@@ -233,11 +233,19 @@ int  rplb_quantize_f32_i8_dev(const float* x, int8_t* q, uint64_t n, const float
                               const int32_t* zp_dev, void* stream);
 
 /* tensor_quantize_int8_symmetric (src/rpl_quantization.c:77-91) on device
- * buffers: min/max pass, then quantize with params->scale_sym, zero point 0. */
+ * buffers: min/max pass, then quantize with params->scale_sym, zero point 0.
+ * Tensors of up to a few million elements (what fits in the registers of one
+ * resident grid; 16-byte aligned x, 4-byte aligned q) are done in one
+ * cooperative launch that reads the tensor once; larger ones in two kernels. */
 int  rplb_quantize_symmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream);
 
 /* tensor_quantize_int8_asymmetric (src/rpl_quantization.c:93-107). */
 int  rplb_quantize_asymmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream);
+
+/* Whether the two calls above may take their one-launch path (per host thread;
+ * 1 = yes, the default; 0 = always two kernels).  Same results; for
+ * measurements.  Returns the previous setting. */
+int  rplb_quantize_onepass(int which);
 
 /* tensor_quantize_per_channel (src/rpl_quantization.c:134-157): channel c is
  * the contiguous block [c*channel_size, (c+1)*channel_size).  scales and
@@ -378,7 +386,8 @@ int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
 /* Status word of the tensor-core kernels launched by the calling host thread:
  * 0, or the code of the bounded wait that expired (1 stage-free, 2 stage-loaded,
  * 3 accumulator-free, 4 accumulator-ready, 5 rows from another GPU; 6 = a bulk
- * copy of the per-channel quantizer's staged rows did not complete).  Every
+ * copy of the per-channel quantizer's staged rows did not complete, 7 = the
+ * grid barrier of the one-launch per-tensor quantizer).  Every
  * host thread has a word of its own, so a give-up is seen by the thread that
  * launched the kernel (and refuses that thread's next GEMM until cleared).
  * Readable at any time; clear != 0 resets it.  A kernel that gave up leaves
@@ -439,7 +448,10 @@ int  rplb_shard_range(uint64_t n, int world, int rank, uint64_t align, uint64_t*
  * [count, in_features], scales [count] and bias [count] (may be NULL) are this
  * rank's rows, in device memory, and stay the caller's.  With world > 1
  * in_features must be a multiple of 16.  forward, gather and free are
- * collective too (every rank calls them in the same order).
+ * collective too (every rank calls them in the same order).  All calls on one
+ * layer must be issued on one stream, or be ordered by the caller: the layer
+ * owns one activation buffer, which a pass overwrites.  A layer is not meant to
+ * be shared between host threads.
  * ---------------------------------------------------------------------- */
 #define RPLB_NCCL_ID_BYTES 128
 typedef struct rplb_sharded_linear rplb_sharded_linear;

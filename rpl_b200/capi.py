@@ -119,6 +119,7 @@ SIGNATURES = {
     "rplb_quantize_f32_i8_dev": ("rc", [_vp, _vp, _u64, _vp, _vp, _vp]),
     "rplb_quantize_symmetric_f32_i8": ("rc", [_vp, _vp, _u64, _vp, _vp]),
     "rplb_quantize_asymmetric_f32_i8": ("rc", [_vp, _vp, _u64, _vp, _vp]),
+    "rplb_quantize_onepass": (C.c_int, [C.c_int]),
     "rplb_quantize_per_channel_f32_i8": ("rc", [_vp, _vp, _vp, _vp, _u64, _u64, _vp]),
     "rplb_per_channel_staging": (C.c_int, [C.c_int]),
     "rplb_dequantize_i8_f32": ("rc", [_vp, _vp, _u64, _f, _i, _vp]),

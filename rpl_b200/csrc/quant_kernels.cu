@@ -184,6 +184,133 @@ quantize_scalar_kernel(const float* __restrict__ x, int8_t* __restrict__ q, uint
         q[i] = (int8_t)quantize_one(x[i], scale, zp);
 }
 
+// ---------------------------------------------------------------------------
+// Per-tensor quantize in one launch, for tensors that fit in the registers of
+// one resident grid (up to a few million elements): tensor_quantize_int8_symmetric
+// / _asymmetric (src/rpl_quantization.c:77-107) read the tensor twice because the
+// scale depends on every element; here every thread keeps its quads in registers
+// across a grid-wide barrier, so the tensor is read once (5 B/element instead of
+// 9) and one launch replaces two.  The kernel is launched cooperatively (all CTAs
+// resident, guaranteed by the driver); the barrier is a counter in the library's
+// control words with a bounded wait, and the last CTA through puts the counters
+// back to zero.
+__device__ __forceinline__ void block_minmax(float& lo, float& hi, float* s_lo, float* s_hi);    // defined with the per-channel kernels
+
+constexpr int kOnePassQuads = 8;                       // quads per thread kept in registers
+constexpr uint64_t kOnePassCtaQuads = (uint64_t)kThreads * kOnePassQuads;
+
+__global__ void __launch_bounds__(kThreads)
+quantize_onepass_kernel(const float* __restrict__ x, int8_t* __restrict__ q, uint64_t n, uint64_t nquads, int asymmetric,
+                        float2* __restrict__ partials, unsigned int* __restrict__ counters, rplb_qparams* __restrict__ params,
+                        int* __restrict__ status) {
+    __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+    __shared__ int s_abort;
+    const float4* xq = reinterpret_cast<const float4*>(x);
+    const uint64_t base = (uint64_t)blockIdx.x * kOnePassCtaQuads + threadIdx.x;
+    float4 v[kOnePassQuads];
+    float lo = INFINITY, hi = -INFINITY;
+    #pragma unroll
+    for (int u = 0; u < kOnePassQuads; u++) {
+        const uint64_t i = base + (uint64_t)u * kThreads;
+        if (i < nquads) v[u] = __ldcs(xq + i);
+    }
+    #pragma unroll
+    for (int u = 0; u < kOnePassQuads; u++) {
+        const uint64_t i = base + (uint64_t)u * kThreads;
+        if (i < nquads) {
+            lo = fminf(fminf(lo, v[u].x), fminf(v[u].y, fminf(v[u].z, v[u].w)));
+            hi = fmaxf(fmaxf(hi, v[u].x), fmaxf(v[u].y, fmaxf(v[u].z, v[u].w)));
+        }
+    }
+    // The up to three elements that do not fill a quad: thread t of CTA 0 takes element 4 nquads + t.
+    float tail = 0.0f;
+    const bool has_tail = blockIdx.x == 0 && nquads * 4 + threadIdx.x < n;
+    if (has_tail) { tail = x[nquads * 4 + threadIdx.x]; lo = fminf(lo, tail); hi = fmaxf(hi, tail); }
+    if (threadIdx.x == 0) s_abort = 0;
+    block_minmax(lo, hi, s_lo, s_hi);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = make_float2(lo, hi);
+        __threadfence();
+        atomicAdd(&counters[0], 1u);
+        // Grid-wide barrier: every CTA is resident (cooperative launch), so this ends; bounded all the same.
+        const long long t0 = clock64();
+        while (*reinterpret_cast<volatile unsigned int*>(&counters[0]) < gridDim.x) {
+            if (clock64() - t0 > 2000000000LL) { s_abort = 1; atomicCAS(status, 0, 7); break; }
+            __nanosleep(64);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    if (s_abort) return;
+    lo = INFINITY; hi = -INFINITY;
+    for (unsigned int j = threadIdx.x; j < gridDim.x; j += kThreads) {
+        const float2 p = __ldcg(partials + j);
+        lo = fminf(lo, p.x);
+        hi = fmaxf(hi, p.y);
+    }
+    __syncthreads();                                   // s_lo / s_hi are reused
+    block_minmax(lo, hi, s_lo, s_hi);
+    // Every CTA derives the same parameters from the same pairs; CTA 0 also writes them out.
+    __shared__ rplb_qparams s_params;
+    if (threadIdx.x == 0) {
+        finalize_params(lo, hi, n ? x[0] : 0.0f, &s_params);
+        if (blockIdx.x == 0) *params = s_params;
+        // Leave the counters as they were found: the last CTA to get here resets them.
+        if (atomicAdd(&counters[1], 1u) == gridDim.x - 1) { counters[0] = 0; counters[1] = 0; }
+    }
+    __syncthreads();
+    const QuantConsts qc = make_quant_consts(asymmetric ? s_params.scale_asym : s_params.scale_sym, asymmetric ? s_params.zp_asym : 0);
+    uint32_t* out = reinterpret_cast<uint32_t*>(q);
+    #pragma unroll
+    for (int u = 0; u < kOnePassQuads; u++) {
+        const uint64_t i = base + (uint64_t)u * kThreads;
+        if (i < nquads) __stcs(out + i, quantize_quad_packed(v[u], qc));
+    }
+    if (has_tail) q[nquads * 4 + threadIdx.x] = (int8_t)quantize_one(tail, qc.scale, qc.zp);
+}
+
+// How many CTAs of the kernel above can be resident on the current device (0 = cooperative launches unsupported).
+static unsigned int onepass_capacity() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < 64 && cached[dev].load() != 0) return (unsigned int)(cached[dev].load() > 0 ? cached[dev].load() : 0);
+    int coop = 0, per_sm = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess) coop = 0;
+    if (coop && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_onepass_kernel, kThreads, 0) != cudaSuccess) per_sm = 0;
+    cudaGetLastError();
+    const int cap = coop ? per_sm * sm_count() : 0;
+    if (dev >= 0 && dev < 64) cached[dev].store(cap > 0 ? cap : -1);
+    return cap > 0 ? (unsigned int)cap : 0;
+}
+
+// 1 = the one-launch path may be taken (per host thread; rplb_quantize_onepass switches it off for measurements).
+static thread_local int t_onepass = 1;
+
+// Tries the one-launch path; *done = false when the tensor does not qualify (too large, unaligned).
+static int launch_quantize_onepass(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, int asymmetric, cudaStream_t st, bool* done) {
+    *done = false;
+    if (!t_onepass || n < 4 || !x || !q || !params) return 0;
+    if (((uintptr_t)x & 15) || ((uintptr_t)q & 3)) return 0;
+    const uint64_t nquads = n / 4;
+    const uint64_t ctas = (nquads + kOnePassCtaQuads - 1) / kOnePassCtaQuads;
+    const unsigned int cap = onepass_capacity();
+    if (cap == 0 || ctas > cap) return 0;
+    Scratch sc;
+    if (int rc = scratch_for(st, (size_t)ctas * sizeof(float2), &sc)) return rc;
+    int* status_dev = kernel_status_word_device();
+    if (!status_dev) return fail(RPLB_E_NO_DEVICE, "could not allocate the kernel status word");
+    float2* partials = static_cast<float2*>(sc.data);
+    unsigned int* counters = sc.control + 2;            // words 2 and 3 of the control block (zero at rest)
+    uint64_t n_arg = n, nq_arg = nquads;
+    void* args[] = {(void*)&x, (void*)&q, (void*)&n_arg, (void*)&nq_arg, (void*)&asymmetric, (void*)&partials, (void*)&counters,
+                    (void*)&params, (void*)&status_dev};
+    if (int rc = cuda_ok(cudaLaunchCooperativeKernel((const void*)quantize_onepass_kernel, dim3((unsigned int)ctas), dim3(kThreads), args, 0, st),
+                         "cudaLaunchCooperativeKernel(quantize_onepass_kernel)")) return rc;
+    *done = true;
+    return launched("quantize_onepass_kernel");
+}
+
 static int launch_quantize(const float* x, int8_t* q, uint64_t n, float scale, int32_t zp,
                            const float* scale_dev, const int32_t* zp_dev, bool reverse, cudaStream_t st) {
     if (n == 0) return 0;
@@ -589,12 +716,24 @@ int rplb_quantize_f32_i8_dev(const float* x, int8_t* q, uint64_t n, const float*
     return launch_quantize(x, q, n, 0.0f, 0, scale_dev, zp_dev, false, as_stream(stream));
 }
 
+int rplb_quantize_onepass(int which) {
+    const int prev = t_onepass;
+    if (which == 0 || which == 1) t_onepass = which;
+    return prev;
+}
+
 int rplb_quantize_symmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream) {
+    bool done = false;
+    if (int rc = launch_quantize_onepass(x, q, n, params, 0, as_stream(stream), &done)) return rc;
+    if (done) return 0;
     if (int rc = launch_minmax(x, n, params, as_stream(stream))) return rc;
     return launch_quantize(x, q, n, 0.0f, 0, &params->scale_sym, nullptr, true, as_stream(stream));
 }
 
 int rplb_quantize_asymmetric_f32_i8(const float* x, int8_t* q, uint64_t n, rplb_qparams* params, void* stream) {
+    bool done = false;
+    if (int rc = launch_quantize_onepass(x, q, n, params, 1, as_stream(stream), &done)) return rc;
+    if (done) return 0;
     if (int rc = launch_minmax(x, n, params, as_stream(stream))) return rc;
     return launch_quantize(x, q, n, 0.0f, 0, &params->scale_asym, &params->zp_asym, true, as_stream(stream));
 }

@@ -238,3 +238,39 @@ def test_scale_from_a_combined_pair_is_the_single_gpu_scale(cuda, lib, port):
     b = torch.stack(got_pair).cpu().numpy()
     want = np.array([port.scale_symmetric(np.float32(-v / 2), np.float32(v)) for v in vals], np.float32)
     assert same(a, want) and same(b, want)
+
+
+@pytest.mark.parametrize("n", [4, 5, 7, 1000, 8192, 8193, 100003, 1 << 20, (1 << 21) + 2, 3500000, 4000000])
+def test_one_launch_and_two_launch_per_tensor_quantize_agree(cuda, lib, port, n):
+    """Tensors that fit in the registers of one resident grid are quantized by one cooperative launch that reads
+    them once; the two-kernel route is the same arithmetic.  Both must give the checker's bits (sizes around the
+    CTA granule, odd tails, a NaN and an outlier far from the rest included); 4000000 exceeds the one-launch limit."""
+    from rpl_b200 import capi, device as D
+    rng = np.random.default_rng(n)
+    x = sweep_tensor(rng, n)
+    if n > 10:
+        x[n // 3] = np.nan
+        x[n - 1] = -77.5
+    wq, ws = port.quantize_symmetric(x)
+    aq, asc, azp = port.quantize_asymmetric(x)
+    L = capi.load()
+    for onepass in (1, 0):
+        prev = L.rplb_quantize_onepass(onepass)
+        try:
+            launches = D.launch_count()
+            q, p = D.quantize_symmetric(dev(x, cuda))
+            used = D.launch_count() - launches
+            q2, p2 = D.quantize_asymmetric(dev(x, cuda))
+            torch.cuda.synchronize()
+        finally:
+            L.rplb_quantize_onepass(prev)
+        assert D.kernel_status(True) == 0
+        assert same(host(q), wq) and same(host(p)[D.QPARAM_SCALE_SYM], ws), onepass
+        assert same(host(q2), aq) and same(host(p2)[D.QPARAM_SCALE_ASYM], asc), onepass
+        assert int(host(p2).view(np.int32)[D.QPARAM_ZP_ASYM]) == azp
+        if onepass and n <= 3500000:
+            assert used == 1                                   # one kernel, not two or three
+    # back to back on one stream: the barrier's counters are left at zero
+    for _ in range(3):
+        q, p = D.quantize_symmetric(dev(x, cuda))
+    assert same(host(q), wq)
