@@ -60,6 +60,8 @@ def parse_args():
                     "(default: on the CPUs next to the rank's GPU)")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep the even column split instead of re-splitting the columns "
                     "in proportion to each GPU's GEMM speed measured during warm-up")
+    ap.add_argument("--transfer", type=int, default=0, help="N > 1: how the int8 rows reach the other ranks: 0 copy engines (default), "
+                    "1 stores from a second quantize kernel (comparison)")
     ap.add_argument("--balance-threshold", type=float, default=1.04,
                     help="N > 1: re-split the columns only when the slowest rank's GEMM takes this many times the fastest's")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
@@ -586,6 +588,8 @@ def run_ours(a):
             st.layer = None
         else:
             st.layer = RowShardedLinear(st.wq, st.wsc, None, n_total=N, max_rows=M, rank=rank, world=world, column_counts=column_counts)
+            if a.transfer:
+                st.layer.transfer(a.transfer)
 
     build(None)
 

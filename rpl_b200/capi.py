@@ -148,6 +148,7 @@ SIGNATURES = {
     "rplb_sharded_linear_forward": ("rc", [_vp, _vp, _u64, _vp, _u64, C.c_int, _vp]),
     "rplb_sharded_linear_quantize": ("rc", [_vp, _vp, _u64, _vp]),
     "rplb_sharded_linear_gemm": ("rc", [_vp, _u64, _vp, _u64, C.c_int, _vp]),
+    "rplb_sharded_linear_transfer": ("rc", [_vp, C.c_int]),
     "rplb_sharded_linear_activation": ("rc", [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "rplb_sharded_linear_gather": ("rc", [_vp, _vp, _u64, _u64, _vp, _vp]),
     "rplb_sharded_linear_submit_host": ("rc", [_vp, _vp, _u64, _vp, C.c_int, C.c_int, _vp]),

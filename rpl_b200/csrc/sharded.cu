@@ -100,6 +100,39 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t value, uint32_t n) {
     if (i < n) dst[i] = value;
 }
 
+// The other way to send the rows: quantize this rank's fp32 rows once more and store the packed int8 straight into
+// the other ranks' activation buffers (plain 16-byte stores over NVLink, 512 contiguous bytes per warp), then set the
+// arrival word of each 128-row block in every destination.  One CTA per 128-row block; the block's word is written
+// after a CTA-wide barrier and a system-scope fence, so it cannot overtake the rows.  Kept beside the copy-engine
+// route for comparison (rplb_sharded_linear_transfer): it costs SM time and a second read of the rows, the copy
+// engines cost neither.
+struct PeerRows {
+    int8_t* xq[7];
+    uint32_t* words[7];
+    int n;
+};
+
+__global__ void __launch_bounds__(512)
+quantize_rows_to_peers_kernel(const float* __restrict__ x, uint64_t rows, uint64_t K, uint64_t row0, const float* __restrict__ scale,
+                              PeerRows peers, uint32_t epoch) {
+    const QuantConsts qc = make_quant_consts(__ldg(scale), 0);
+    const uint64_t first = (uint64_t)blockIdx.x * 128, last = first + 128 < rows ? first + 128 : rows;
+    const uint64_t pieces = (last - first) * K / 16;                          // 16 int8 = four quads per piece (K % 16 == 0)
+    const float4* src = reinterpret_cast<const float4*>(x + first * K);
+    for (uint64_t i = threadIdx.x; i < pieces; i += blockDim.x) {
+        const float4 a = __ldcs(src + 4 * i), b = __ldcs(src + 4 * i + 1), c = __ldcs(src + 4 * i + 2), d = __ldcs(src + 4 * i + 3);
+        const uint4 w = make_uint4(quantize_quad_packed(a, qc), quantize_quad_packed(b, qc), quantize_quad_packed(c, qc), quantize_quad_packed(d, qc));
+        const uint64_t at = (row0 + first) * K + 16 * i;
+        for (int p = 0; p < peers.n; p++) *reinterpret_cast<uint4*>(peers.xq[p] + at) = w;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint64_t block = (row0 + first) / 128;
+        for (int p = 0; p < peers.n; p++) *reinterpret_cast<volatile uint32_t*>(peers.words[p] + block) = epoch;
+    }
+}
+
 // Where each rank's column block begins (entry `world` = the total): passed to kernels by value.
 struct ColumnSplit {
     uint64_t begin[9];
@@ -155,6 +188,7 @@ struct ShardedLinear {
     cudaStream_t s_push = nullptr;
     cudaEvent_t ev_quantized = nullptr, ev_pushed = nullptr;
     bool pushed = false;
+    int transfer = 0;                        // 0 = peer copies by the copy engines, 1 = stores from a quantize kernel
     // gather
     float* landing = nullptr;
     size_t landing_bytes = 0;
@@ -333,7 +367,17 @@ static int quantize_and_send(ShardedLinear* h, const float* x_local, uint64_t M,
     }
     if (int e = cuda_ok(cudaEventRecord(h->ev_quantized, st), "cudaEventRecord")) return e;
     if (int e = cuda_ok(cudaStreamWaitEvent(h->s_push, h->ev_quantized, 0), "cudaStreamWaitEvent")) return e;
-    if (nt) {
+    if (nt && h->transfer == 1) {
+        PeerRows peers = {};
+        for (int d = 1; d < h->world; d++) {
+            const int peer = (h->rank - d + h->world) % h->world;
+            peers.xq[peers.n] = h->peer_xq(peer);
+            peers.words[peers.n] = h->peer_words(peer);
+            peers.n++;
+        }
+        quantize_rows_to_peers_kernel<<<nt, 512, 0, h->s_push>>>(x_local, rc, h->K, r0, &h->params->scale_sym, peers, h->epoch);
+        if (int e = launched("quantize_rows_to_peers_kernel")) return e;
+    } else if (nt) {
         // Rank r - 1 reaches these rows first (every rank walks the blocks upwards from its own), then r - 2, ...
         for (int d = 1; d < h->world; d++) {
             const int peer = (h->rank - d + h->world) % h->world;
@@ -366,6 +410,13 @@ static int gemm_rows(ShardedLinear* h, uint64_t M, uint64_t b0, uint64_t b1, flo
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "sharded linear over several GPUs: the tensor-core kernel cannot take this shape or alignment");
     return gemm_tcgen05(p, st, 1);
+}
+
+// With the kernel-store route the caller's fp32 rows are read on the side stream: the caller's stream must not run
+// ahead of that read (its next work may overwrite the rows).
+static int after_gemm(ShardedLinear* h, cudaStream_t st) {
+    if (h->world > 1 && h->transfer == 1 && h->pushed) return cuda_ok(cudaStreamWaitEvent(st, h->ev_pushed, 0), "cudaStreamWaitEvent");
+    return 0;
 }
 
 static int check_call(const ShardedLinear* h, uint64_t M, const void* out, uint64_t ldo) {
@@ -508,7 +559,8 @@ int rplb_sharded_linear_forward(rplb_sharded_linear* layer, const float* x_local
     if (int e = check_call(h, rows, out, ldo)) return e;
     cudaStream_t st = as_stream(stream);
     if (int e = quantize_and_send(h, x_local, rows, st)) return e;
-    return gemm_rows(h, rows, 0, rows, out, ldo, relu, st);
+    if (int e = gemm_rows(h, rows, 0, rows, out, ldo, relu, st)) return e;
+    return after_gemm(h, st);
 }
 
 int rplb_sharded_linear_quantize(rplb_sharded_linear* layer, const float* x_local, uint64_t rows, void* stream) {
@@ -522,7 +574,17 @@ int rplb_sharded_linear_quantize(rplb_sharded_linear* layer, const float* x_loca
 int rplb_sharded_linear_gemm(rplb_sharded_linear* layer, uint64_t rows, float* out, uint64_t ldo, int relu, void* stream) {
     ShardedLinear* h = reinterpret_cast<ShardedLinear*>(layer);
     if (int e = check_call(h, rows, out, ldo)) return e;
-    return gemm_rows(h, rows, 0, rows, out, ldo, relu, as_stream(stream));
+    if (int e = gemm_rows(h, rows, 0, rows, out, ldo, relu, as_stream(stream))) return e;
+    return after_gemm(h, as_stream(stream));
+}
+
+int rplb_sharded_linear_transfer(rplb_sharded_linear* layer, int which) {
+    ShardedLinear* h = reinterpret_cast<ShardedLinear*>(layer);
+    if (!h) return fail(RPLB_E_BAD_ARG, "sharded linear: null handle");
+    if (which != 0 && which != 1) return fail(RPLB_E_BAD_ARG, "rplb_sharded_linear_transfer: 0 (copy engines) or 1 (stores from a kernel)");
+    if (which == 1 && h->K % 16 != 0) return fail(RPLB_E_UNSUPPORTED, "stores from a kernel need in_features %% 16 == 0");
+    h->transfer = which;
+    return 0;
 }
 
 int rplb_sharded_linear_activation(const rplb_sharded_linear* layer, const int8_t** xq, const float** scale) {
@@ -615,6 +677,7 @@ int rplb_sharded_linear_submit_host(rplb_sharded_linear* layer, const float* x_l
         if (N) if (int e = cuda_ok(cudaMemcpyAsync(out + b0 * N, dout + b0 * N, (size_t)(b1 - b0) * N * 4, cudaMemcpyDeviceToHost, h->s_out),
                                    "cudaMemcpyAsync(download)")) return e;
     }
+    if (int e = after_gemm(h, st)) return e;
     if (int e = cuda_ok(cudaEventRecord(h->ev_computed[i], st), "cudaEventRecord")) return e;
     if (int e = cuda_ok(cudaEventRecord(h->ev_downloaded[i], h->s_out), "cudaEventRecord")) return e;
     h->slot_used[i] = true;

@@ -525,6 +525,10 @@ class RowShardedLinear:
                         1 if relu else 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
         return out
 
+    def transfer(self, which):
+        """0 = the int8 rows travel by copy-engine peer copies (default), 1 = by stores from a second quantize kernel."""
+        self._capi.call("rplb_sharded_linear_transfer", self.handle, int(which))
+
     def activation(self, M):
         """The whole int8 activation as this rank holds it after a forward, and its scale (views, not copies)."""
         C = self._C

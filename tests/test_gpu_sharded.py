@@ -189,17 +189,20 @@ def _rank_main(rank, world, port_no, result_dir):
         layer = RowShardedLinear(wq, ws, torch.from_numpy(bias[b:b + c]).to(dev_), n_total=n_total, max_rows=max_rows,
                                  rank=rank, world=world, column_counts=counts)
         assert (layer.col_begin, layer.col_count) == (b, c)
-        M = 900
-        x = rng.standard_normal((M, K)).astype(np.float32)
-        r0, rc = layer.rows(M)
-        out = layer.forward(torch.from_numpy(x[r0:r0 + rc]).to(dev_), M)
-        full = layer.gather(out, M)
-        torch.cuda.synchronize()
-        hq, hs = cpu.quantize_symmetric(x)
-        want_full = cpu.linear_dequant(hq, hwq, hs, hws, bias, relu=False)
-        assert np.array_equal(out.cpu().numpy().view(np.uint32), want_full[:, b:b + c].view(np.uint32)), "uneven split, rank %d" % rank
-        assert np.array_equal(full.cpu().numpy().view(np.uint32), want_full.view(np.uint32)), "gather with an uneven split, rank %d" % rank
-        assert D.kernel_status(True) == 0
+        for M, route in ((900, 0), (1100, 1), (640, 1), (900, 0)):       # route 1: the rows travel by stores from a kernel
+            layer.transfer(route)
+            x = rng.standard_normal((M, K)).astype(np.float32)
+            r0, rc = layer.rows(M)
+            out = layer.forward(torch.from_numpy(np.ascontiguousarray(x[r0:r0 + rc])).to(dev_), M)
+            full = layer.gather(out, M)
+            torch.cuda.synchronize()
+            hq, hs = cpu.quantize_symmetric(x)
+            xq, _ = layer.activation(M)
+            assert np.array_equal(xq.cpu().numpy(), hq), "int8 activation, route %d, rank %d" % (route, rank)
+            want_full = cpu.linear_dequant(hq, hwq, hs, hws, bias, relu=False)
+            assert np.array_equal(out.cpu().numpy().view(np.uint32), want_full[:, b:b + c].view(np.uint32)), "uneven split, rank %d" % rank
+            assert np.array_equal(full.cpu().numpy().view(np.uint32), want_full.view(np.uint32)), "gather with an uneven split, rank %d" % rank
+            assert D.kernel_status(True) == 0
         dist.barrier()
         layer.close()
         with open(os.path.join(result_dir, "ok%d" % rank), "w") as f:
