@@ -486,7 +486,7 @@ int  rplb_sharded_linear_gemm(rplb_sharded_linear* layer, uint64_t rows, float* 
 /* How a rank's int8 rows reach the other ranks: 0 (default) = one peer copy per destination by the copy engines,
  * nearest consumer first, no SM involved; 1 = a second quantize kernel on a side stream stores the packed rows
  * straight into every destination (plain stores over NVLink).  Same results; every rank must choose the same.
- * Measured on 2 and 4 B200s the copy engines are the faster route (the kernel takes SM time from the GEMM and
+ * Measured on 2 B200s the copy engines are the faster route (the kernel takes SM time from the GEMM and
  * reads the fp32 rows a second time), so they are the default. */
 int  rplb_sharded_linear_transfer(rplb_sharded_linear* layer, int which);
 /* After a forward: the whole int8 activation [rows, in_features] as this rank
