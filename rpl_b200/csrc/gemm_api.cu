@@ -210,8 +210,10 @@ int rplb_linear_i8_dequant_f32_absmax(const int8_t* x, const int8_t* w, float* o
     p.A = x; p.B = w; p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo;
     p.b_is_kn = 0; p.mode = EPI_DEQUANT_F32;
     p.a_scale = a_scale; p.w_scales = w_scales; p.bias_f32 = bias; p.relu = relu; p.absmax_out = absmax;
+    int folded = 0;
+    p.next_scale = next_scale; p.next_scale_done = &folded;
     if (int rc = run_gemm(p, st)) return rc;
-    if (next_scale) {
+    if (next_scale && !folded) {
         absmax_to_scale_kernel<<<1, 1, 0, st>>>(absmax, next_scale);
         return launched("absmax_to_scale_kernel");
     }
@@ -263,8 +265,10 @@ int rplb_quantize_linear_dequant_f32(const float* x, const int8_t* w, float* out
         return fail(RPLB_E_UNSUPPORTED, "%s: needs N <= 128 with K <= 896 and K %% 16 == 0, or N <= 16 with K <= 512 and K %% 4 == 0; "
                     "quantize into a buffer and call rplb_linear_i8_dequant_f32 instead", who);
     if (absmax) if (int rc = cuda_ok(cudaMemsetAsync(absmax, 0, sizeof(float), st), "cudaMemsetAsync(absmax)")) return rc;
+    int folded = 0;
+    p.next_scale = next_scale; p.next_scale_done = &folded;
     if (int rc = small ? quantize_linear_small(x, p, st) : gemm_fused_quant(x, p, st)) return rc;
-    if (next_scale) {
+    if (next_scale && !folded) {
         absmax_to_scale_kernel<<<1, 1, 0, st>>>(absmax, next_scale);
         return launched("absmax_to_scale_kernel");
     }
@@ -289,7 +293,8 @@ int rplb_linear_i8_dequant_f32_arriving(const int8_t* x, const int8_t* w, float*
     // Only the tensor-core kernel waits for arriving rows; there is no other route.
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "%s: needs K %% 16 == 0 and 16-byte aligned x and w", who);
-    return gemm_tcgen05(p, as_stream(stream), 1);
+    const int asked = t_backend;         // 5: the 256 x 256 kernel, 3: the 128 x 256 kernel, else the library's choice of the two
+    return gemm_tcgen05(p, as_stream(stream), asked == 3 ? 1 : asked == 5 ? 3 : 0);
 }
 
 int rplb_linear_i8_requant_i8(const int8_t* x, const int8_t* w, int8_t* out, uint64_t M, uint64_t K, uint64_t N,

@@ -34,6 +34,12 @@ struct GemmProblem {
     const float* bias_f32;    // N floats or null
     int relu;
     float* absmax_out;        // optional: max |out| over the call is folded in here (bits of a non-negative float)
+    // Optional, with absmax_out: the next layer's activation scale, *absmax_out / 127 (src/rpl_quantization.c:87-88).
+    // A launcher whose kernel writes it (its last warp through, counted on `ticket`, a device word that is zero at
+    // rest) sets *next_scale_done, a host flag; otherwise the caller launches the one-thread kernel that divides.
+    float* next_scale;
+    unsigned int* ticket;
+    int* next_scale_done;
     // EPI_DEQUANT_I8
     const float* out_scale;   // one float on the device
     int32_t out_zp;

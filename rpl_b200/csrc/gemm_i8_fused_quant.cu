@@ -260,6 +260,16 @@ gemm_i8_fused_quant_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         }
         if (tma && lane == 0) bulk_wait_all();
         if (p.absmax_out) absmax_publish(p.absmax_out, absmax);
+        if (p.next_scale && lane == 0) {
+            // The last epilogue warp of the grid turns the maximum into the next layer's scale.
+            __threadfence();
+            if (atomicAdd(p.ticket, 1u) == gridDim.x * (uint32_t)(FQ_CONVERTER_WARP0 - FQ_EPILOGUE_WARP0) - 1u) {
+                __threadfence();
+                const float top = __uint_as_float(atomicOr(reinterpret_cast<unsigned int*>(p.absmax_out), 0u));
+                *p.next_scale = __fdiv_rn(top, 127.0f);
+                *p.ticket = 0;                  // leave the control word as it was found
+            }
+        }
     } else if (QUANT) {
         // ------------------------------------------------------------- converters: fp32 slot -> int8 rows of the stage
         const int cw = warp - FQ_CONVERTER_WARP0;
@@ -355,8 +365,17 @@ static int launch_narrow(const void* x, const GemmProblem& p, cudaStream_t st) {
     unsigned int sms = (unsigned int)sm_count();
     if (sms == 0) sms = 148;
     const unsigned int grid = tiles_m < sms ? tiles_m : sms;
+    GemmProblem q = p;
+    q.ticket = nullptr;
+    if (q.next_scale && q.absmax_out) {
+        // The counter of finished warps lives in the stream's scratch block (control word 8, zero at rest).
+        Scratch sc;
+        if (scratch_for(st, 0, &sc) == 0) q.ticket = sc.control + 8;
+    }
+    if (!q.ticket) q.next_scale = nullptr;
     gemm_i8_fused_quant_kernel<QUANT><<<grid, QUANT ? FQ_THREADS : FQ_CONVERTER_WARP0 * 32, fq_smem_bytes(num_kb), st>>>(
-        mw, mx, mo, p, tiles_m, num_kb, tma_out, status_dev);
+        mw, mx, mo, q, tiles_m, num_kb, tma_out, status_dev);
+    if (q.next_scale && p.next_scale_done) *p.next_scale_done = 1;
     return launched(QUANT ? "gemm_i8_fused_quant_kernel<quantize>" : "gemm_i8_fused_quant_kernel<int8>");
 }
 

@@ -146,12 +146,15 @@ constexpr int SMALL_WARPS = 8;
 template <int NT>                      // the number of output features, known at compile time: the inner loop has no tests
 __global__ void __launch_bounds__(SMALL_WARPS * 32, 2)
 quantize_linear_small_kernel(const float* __restrict__ x, const GemmProblem p) {
-    __shared__ uint32_t w_words[SMALL_N_MAX * SMALL_K_MAX / 4];          // [N][K/4]
+    constexpr uint32_t N = NT, NP = (NT + 3) & ~3;                       // N padded to whole 16-byte pieces
+    __shared__ __align__(16) uint32_t w_words[SMALL_N_MAX * SMALL_K_MAX / 4];   // [K/4][NP]: word t of every output feature side by side
     __shared__ uint32_t tiles[SMALL_WARPS][32 * 33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t N = NT;
     const uint32_t K = (uint32_t)p.K, kw = K / 4;
-    for (uint32_t i = threadIdx.x; i < N * kw; i += blockDim.x) w_words[i] = __ldg(reinterpret_cast<const uint32_t*>(p.B) + i);
+    for (uint32_t i = threadIdx.x; i < NP * kw; i += blockDim.x) {
+        const uint32_t n = i / kw, t = i % kw;
+        w_words[t * NP + n] = n < N ? __ldg(reinterpret_cast<const uint32_t*>(p.B) + (size_t)n * kw + t) : 0u;
+    }
     __syncthreads();
     const QuantConsts qc = make_quant_consts(__ldg(p.a_scale), 0);
     const float a_scale = qc.scale;
@@ -183,8 +186,15 @@ quantize_linear_small_kernel(const float* __restrict__ x, const GemmProblem p) {
             const uint32_t words = min(32u, kw - c0);
             for (uint32_t t = 0; t < words; t++) {
                 const int a = (int)tile[lane * 33 + t];                  // row `lane`, word c0 + t
+                const uint4* wt = reinterpret_cast<const uint4*>(w_words + (size_t)(c0 + t) * NP);   // the same words for every lane
+                uint32_t wv[NP];
                 #pragma unroll
-                for (int n = 0; n < NT; n++) acc[n] = __dp4a(a, (int)w_words[n * kw + c0 + t], acc[n]);
+                for (uint32_t q = 0; q < NP / 4; q++) {
+                    const uint4 u = wt[q];
+                    wv[4 * q] = u.x; wv[4 * q + 1] = u.y; wv[4 * q + 2] = u.z; wv[4 * q + 3] = u.w;
+                }
+                #pragma unroll
+                for (int n = 0; n < NT; n++) acc[n] = __dp4a(a, (int)wv[n], acc[n]);
             }
         }
         const uint64_t m = m0 + lane;

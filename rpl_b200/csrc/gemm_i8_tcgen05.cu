@@ -478,6 +478,8 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     WideShared* sh = reinterpret_cast<WideShared*>(epi_tiles + EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
+    // Walk the m-tiles starting at the tile that holds the first block of A in place at launch.
+    const uint32_t rotate = p.a_ready ? p.a_local_first / 2 : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWideStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
@@ -502,7 +504,15 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 uint32_t tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M);
+                tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M, rotate);
+                if (p.a_ready) {
+                    // A 256-row tile spans two arrival words; rows that come from another GPU must have landed.
+                    const uint32_t blocks = (uint32_t)((p.M + 127) / 128);
+                    for (uint32_t b = 2 * tm; ok && b < 2 * tm + 2 && b < blocks; b++)
+                        if (!(b - p.a_local_first < p.a_local_count))
+                            ok = wait_rows_ready(p.a_ready + b, p.a_epoch, &sh->abort_flag, status);
+                    if (!ok) break;
+                }
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait_bounded(&sh->empty[stage], phase ^ 1, &sh->abort_flag, status, TC_WAIT_EMPTY)) { ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)stage * WIDE_STAGE_BYTES;
@@ -561,7 +571,7 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         uint32_t acc_phase = 0;
         for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M);
+            tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M, rotate);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
             if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             bool ok = mbar_wait_bounded(&sh->acc_full, acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
@@ -950,13 +960,15 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
             return fail(RPLB_E_UNSUPPORTED, "peer destinations need the fp32 epilogue, W as [N,K] and at most %d peers", kMaxPeers);
         variant = 1;
     }
+    // A GEMM long enough for the board to settle on its power cap: what counts then is work per joule.
+    const bool sustained = (double)p.M * (double)p.N * (double)p.K >= 1.1e12;
     if (p.a_ready) {
-        // Only the 128 x 256 kernel waits for rows that are still arriving.
+        // The 128 x 256 kernel and the 256 x 256 kernel wait for rows that are still arriving.
         const uint64_t tiles_m = (p.M + TILE_M - 1) / TILE_M;
         if (p.b_is_kn || (uint64_t)p.a_local_first + p.a_local_count > tiles_m || (p.a_local_first >= tiles_m && tiles_m))
             return fail(RPLB_E_BAD_ARG, "arriving rows: local blocks [%u, +%u) outside the %llu row blocks of A",
                         p.a_local_first, p.a_local_count, (unsigned long long)tiles_m);
-        variant = 1;
+        variant = (variant == 3 || (variant == 0 && sustained)) ? 3 : 1;
     }
     if (variant == 4) return gemm_narrow(p, st);         // asked for by name: refused if the shape does not fit
     if (variant == 0 && gemm_narrow_supports(p) && p.M >= (uint64_t)TILE_M * sms) {
@@ -967,14 +979,16 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     }
     if (variant == 0) {
         // Measured on B200 (1000 W cap): un-throttled, the pair kernel keeps the
-        // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster;
-        // in a long run both sit at the power cap and the single-CTA kernel does
-        // ~6 % more work per joule.  So: the pair kernel for GEMMs short enough
-        // to finish before the power governor reacts, provided every pair of SMs
-        // gets a 256 x 256 tile of its own; the single-CTA kernel otherwise.
+        // tensor pipe busier (86 % against 71 % of cycles) and is ~10 % faster than
+        // the 128 x 256 kernel; in a long run every kernel sits at the power cap and
+        // the order is work per joule: the 256 x 256 single-CTA kernel (a third less
+        // operand traffic into the SM) runs at ~1.42 GHz against ~1.38 GHz and is
+        // ~4 % faster than the 128 x 256 kernel, which in turn beats the pair kernel
+        // by ~6 %.  So: the 256 x 256 kernel for GEMMs long enough for the governor
+        // to settle; the pair kernel for shorter ones, provided every pair of SMs
+        // gets a 256 x 256 tile of its own; the 128 x 256 kernel otherwise.
         const uint64_t pair_tiles = ((p.M + PAIR_TILE_M - 1) / PAIR_TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
-        const double macs = (double)p.M * (double)p.N * (double)p.K;
-        variant = (pair_tiles >= sms / 2 && macs < 1.1e12) ? 2 : 1;
+        variant = sustained ? 3 : (pair_tiles >= sms / 2 ? 2 : 1);
     }
     CUtensorMap ma, mw, mo;
     int tma_out = 0;

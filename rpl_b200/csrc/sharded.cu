@@ -409,7 +409,10 @@ static int gemm_rows(ShardedLinear* h, uint64_t M, uint64_t b0, uint64_t b1, flo
     if (hi > lo) { p.a_local_first = (uint32_t)((lo - b0) / 128); p.a_local_count = (uint32_t)((hi - lo + 127) / 128); }
     if (!gemm_tcgen05_supports(p))
         return fail(RPLB_E_UNSUPPORTED, "sharded linear over several GPUs: the tensor-core kernel cannot take this shape or alignment");
-    return gemm_tcgen05(p, st, 1);
+    // The library's own choice between the two kernels that can wait for rows (256 x 256 tiles for long GEMMs,
+    // 128 x 256 otherwise), unless the thread asked for one of them by name.
+    const int asked = thread_gemm_backend(-1);
+    return gemm_tcgen05(p, st, asked == 3 ? 1 : asked == 5 ? 3 : 0);
 }
 
 // With the kernel-store route the caller's fp32 rows are read on the side stream: the caller's stream must not run

@@ -390,6 +390,8 @@ def test_kernel_for_few_output_features(cuda, lib, port, backend, mnk, relu):
         assert D.kernel_status(True) == 0
         assert same(host(got), want), which
         assert same(host(amax)[0], np.float32(np.abs(want).max()))
+        # the scale of the next layer's activation, written by the last warp through (no second kernel)
+        assert same(host(nxt)[0], np.float32(np.abs(want).max()) / np.float32(127.0))
     D.gemm_backend(TC_NARROW)
     with pytest.raises(capi.RplError):                       # other epilogues and wider layers are refused, not emulated
         D.linear_i8(dev(A, cuda), dev(W, cuda))

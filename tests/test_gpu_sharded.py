@@ -38,9 +38,12 @@ def _problem(M, N, K, seed):
 
 @pytest.mark.parametrize("mnk,first,count", [((1000, 300, 256), 3, 2), ((128, 256, 128), 0, 1), ((700, 520, 784), 5, 1),
                                              ((1024, 256, 512), 0, 0), ((2048, 512, 256), 12, 4)])
-def test_arriving_rows_with_words_already_set(cuda, lib, port, mnk, first, count):
-    """Same bits as the plain call whatever block the walk starts from."""
+@pytest.mark.parametrize("which", [3, 5])
+def test_arriving_rows_with_words_already_set(cuda, lib, port, mnk, first, count, which):
+    """Same bits as the plain call whatever block the walk starts from, from both kernels that can wait for rows
+    (128-row tiles: one arrival word each; 256-row tiles: two)."""
     from rpl_b200 import device as D
+    prev = D.gemm_backend(which)
     M, N, K = mnk
     xq, wq, ws, bias = _problem(M, N, K, M + N + K)
     sa = np.float32(0.0173)
@@ -52,6 +55,7 @@ def test_arriving_rows_with_words_already_set(cuda, lib, port, mnk, first, count
     got = D.linear_i8_dequant_arriving(dev(xq, cuda), dev(wq, cuda), torch.tensor([sa], device=cuda), dev(ws, cuda), ready,
                                        epoch, first, count, bias=dev(bias, cuda), relu=True)
     torch.cuda.synchronize()
+    D.gemm_backend(prev)
     assert D.kernel_status(True) == 0
     assert same(got.cpu().numpy(), want)
 
@@ -189,8 +193,10 @@ def _rank_main(rank, world, port_no, result_dir):
         layer = RowShardedLinear(wq, ws, torch.from_numpy(bias[b:b + c]).to(dev_), n_total=n_total, max_rows=max_rows,
                                  rank=rank, world=world, column_counts=counts)
         assert (layer.col_begin, layer.col_count) == (b, c)
-        for M, route in ((900, 0), (1100, 1), (640, 1), (900, 0)):       # route 1: the rows travel by stores from a kernel
+        # route 1: the rows travel by stores from a kernel; kernel 5: 256-row tiles, two arrival words per tile
+        for M, route, kernel in ((900, 0, 0), (1100, 1, 5), (640, 1, 0), (900, 0, 5)):
             layer.transfer(route)
+            D.gemm_backend(kernel)
             x = rng.standard_normal((M, K)).astype(np.float32)
             r0, rc = layer.rows(M)
             out = layer.forward(torch.from_numpy(np.ascontiguousarray(x[r0:r0 + rc])).to(dev_), M)
@@ -203,6 +209,7 @@ def _rank_main(rank, world, port_no, result_dir):
             assert np.array_equal(out.cpu().numpy().view(np.uint32), want_full[:, b:b + c].view(np.uint32)), "uneven split, rank %d" % rank
             assert np.array_equal(full.cpu().numpy().view(np.uint32), want_full.view(np.uint32)), "gather with an uneven split, rank %d" % rank
             assert D.kernel_status(True) == 0
+        D.gemm_backend(0)
         dist.barrier()
         layer.close()
         with open(os.path.join(result_dir, "ok%d" % rank), "w") as f:
