@@ -842,9 +842,11 @@ def run_ours(a):
             dist.destroy_process_group()
         return
 
-    # DRAM traffic of the GEMM from an ncu capture at 16384 x 16384 x 8192
-    # (dram read + write): 7.13 B per output element at K = 8192.
-    traffic = 7.13 * M * count if K == 8192 else None
+    # DRAM traffic of the GEMM from ncu captures at 16384 x 16384 x 8192 (dram read + write) per output element
+    # at K = 8192: 9.39 B for the kernel with 256 x 256 tiles (the library's choice for a GEMM this long),
+    # 7.13 B for the kernel with 128 x 256 tiles.
+    wide = a.gemm_backend == 5 or (a.gemm_backend == 0 and float(M) * count * K >= 1.1e12)
+    traffic = (9.39 if wide else 7.13) * M * count if K == 8192 and a.gemm_backend in (0, 3, 5) else None
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
     sched = ("every rank: min/max of its rows, max-all-reduce of (-min, max), quantize its rows, peer copies of the int8 rows "
@@ -865,7 +867,7 @@ def run_ours(a):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                      "frac": achieved / int8_peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by output elements)",
                      "algorithmic_bytes": float(M * K + count * K + 4 * M * count),
-                     "launches_per_step": 1, "kernel": "gemm_i8_tc_kernel",
+                     "launches_per_step": 1, "kernel": "gemm_i8_tc_wide_kernel" if wide else "gemm_i8_tc_kernel",
                      "peak_note": "2 x bf16_tflops_sustained of %s (int8 dense = 2 x bf16 dense)" % peaks["source"],
                      "frac_of_nominal_4500": achieved / 4500.0,
                      "ms_x_mhz": gemm_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None},
