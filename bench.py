@@ -62,7 +62,7 @@ def parse_args():
                     "in proportion to each GPU's GEMM speed measured during warm-up")
     ap.add_argument("--transfer", type=int, default=0, help="N > 1: how the int8 rows reach the other ranks: 0 copy engines (default), "
                     "1 stores from a second quantize kernel (comparison)")
-    ap.add_argument("--balance-threshold", type=float, default=1.04,
+    ap.add_argument("--balance-threshold", type=float, default=1.06,
                     help="N > 1: re-split the columns only when the slowest rank's GEMM takes this many times the fastest's")
     ap.add_argument("--no-clocks", action="store_true", help="no nvidia-smi sampling and no pre-roll (for profiler runs)")
     ap.add_argument("--sweep-only", action="store_true", help="only the quantize/dequantize GB/s figures (for profiler runs)")
