@@ -287,7 +287,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmProblem& p, const CUten
             w[c] = (uint32_t)s;
         }
     }
-    if (tma_out) {
+    // A tensor store clips at the map's edge in whole 16-byte pieces, not in elements (measured: with N % 4 != 0 the
+    // piece that straddles the edge was written in full, up to three columns beyond the block), so the chunk that
+    // holds a ragged edge leaves from registers, element by element.
+    const bool by_tma = tma_out && (full || (n_left & 3) == 0);
+    if (by_tma) {
         if (lane == 0) bulk_wait_read_all();         // the previous chunk has left the tile
         __syncwarp();
         stage_row_swizzled(tile, lane, w);
@@ -310,6 +314,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmProblem& p, const CUten
             }
         }
         if (PEERS) {
+            if (tma_out && lane == 0) bulk_wait_read_all();      // a tensor store of an earlier chunk may still read the tile
             __syncwarp();                            // the previous chunk has been read out of the tile
             stage_row_swizzled(tile, lane, w);
             __syncwarp();

@@ -397,3 +397,65 @@ def test_kernel_for_few_output_features(cuda, lib, port, backend, mnk, relu):
         D.linear_i8(dev(A, cuda), dev(W, cuda))
     with pytest.raises(capi.RplError):
         D.linear_i8_dequant(dev(A[:64], cuda), torch.zeros((256, K), dtype=torch.int8, device=cuda), a_dev, torch.ones(256, device=cuda))
+
+
+def _random_shapes(count, seed):
+    rng = np.random.default_rng(seed)
+    shapes = []
+    for _ in range(count):
+        M = int(rng.integers(1, 900))
+        N = int(rng.integers(1, 700))
+        K = 16 * int(rng.integers(1, 80))                   # the tensor-core kernels need K % 16 == 0
+        shapes.append((M, N, K))
+    return shapes
+
+
+@pytest.mark.parametrize("which", [SIMT, TC_SINGLE, TC_PAIR, TC_WIDE])
+def test_seeded_random_shapes_every_kernel(cuda, lib, port, backend, which):
+    """Sixteen shapes drawn from a fixed seed (ragged M and N, K from 16 to 1264), every contraction kernel, the
+    raw int32 result and the fp32 epilogue with bias and ReLU into a column block of a wider matrix: the same bits
+    as the checker, and nothing written outside the block."""
+    D = backend
+    D.gemm_backend(which)
+    for M, N, K in _random_shapes(16, 20261125):
+        rng = np.random.default_rng(M * 1009 + N * 31 + K)
+        A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+        ws = ((rng.random(N) + 0.5) * 3e-4).astype(np.float32)
+        bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        sa = np.float32(0.0117)
+        assert same(host(D.linear_i8(dev(A, cuda), dev(W, cuda))), port.linear(A, W)), (which, M, N, K)
+        pad = 4 * int(rng.integers(0, 4))                   # a 16-byte multiple keeps the TMA-store path reachable
+        wide = torch.full((M, N + pad + 5), -7.0, device=cuda)
+        got = D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), dev(np.array([sa], np.float32), cuda), dev(ws, cuda), dev(bias, cuda), True,
+                                  out=wide[:, pad:pad + N])
+        want = port.linear_dequant(A, W, sa, ws, bias, True)
+        assert same(host(got), want), (which, M, N, K)
+        assert (host(wide[:, :pad]) == -7.0).all() and (host(wide[:, pad + N:]) == -7.0).all(), (which, M, N, K)
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
+
+
+def test_seeded_random_shapes_kernel_for_few_output_features(cuda, lib, port, backend):
+    """The same sweep for the kernel that keeps the weights in shared memory (N <= 128, K <= 896): column blocks whose
+    width is not a multiple of four leave their ragged edge from registers, not through a tensor store."""
+    D = backend
+    D.gemm_backend(TC_NARROW)
+    rng0 = np.random.default_rng(777)
+    for _ in range(12):
+        M, N, K = int(rng0.integers(1, 1500)), int(rng0.integers(1, 129)), 16 * int(rng0.integers(1, 57))
+        rng = np.random.default_rng(M * 1009 + N * 31 + K)
+        A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+        ws = ((rng.random(N) + 0.5) * 3e-4).astype(np.float32)
+        bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        sa = np.float32(0.0117)
+        pad = 4 * int(rng.integers(0, 4))
+        wide = torch.full((M, N + pad + (4 - N % 4) % 4 + 4), -7.0, device=cuda)       # row stride a multiple of 16 bytes
+        got = D.linear_i8_dequant(dev(A, cuda), dev(W, cuda), dev(np.array([sa], np.float32), cuda), dev(ws, cuda), dev(bias, cuda), True,
+                                  out=wide[:, pad:pad + N])
+        want = port.linear_dequant(A, W, sa, ws, bias, True)
+        assert same(host(got), want), (M, N, K)
+        assert (host(wide[:, :pad]) == -7.0).all() and (host(wide[:, pad + N:]) == -7.0).all(), (M, N, K)
+    torch.cuda.synchronize()
+    assert D.kernel_status(True) == 0
