@@ -125,6 +125,62 @@ def test_row_sharded_layer_on_one_rank(cuda, lib, port, mnk):
     assert D.kernel_status(True) == 0
 
 
+@pytest.mark.parametrize("which", [3, 5])
+def test_arriving_rows_seeded_random_shapes(cuda, lib, port, which):
+    """Random shapes and random local ranges (odd first blocks, ranges that end in the ragged last block) through
+    both kernels that can wait for rows; every word already set, so nothing waits and the result must not depend
+    on where the walk starts."""
+    from rpl_b200 import device as D
+    prev = D.gemm_backend(which)
+    try:
+        rng = np.random.default_rng(2718 + which)
+        for _ in range(10):
+            M, N, K = int(rng.integers(1, 2500)), int(rng.integers(1, 700)), 16 * int(rng.integers(1, 40))
+            xq, wq, ws, bias = _problem(M, N, K, M * 7 + N)
+            sa = np.float32(0.0173)
+            blocks = (M + 127) // 128
+            first = int(rng.integers(0, blocks))
+            count = int(rng.integers(0, blocks - first + 1))
+            epoch = int(rng.integers(1, 1 << 31))
+            ready = torch.full((blocks,), epoch, dtype=torch.int64, device=cuda).to(torch.int32)
+            ready[first:first + count] = 0                     # local blocks are never looked at
+            got = D.linear_i8_dequant_arriving(dev(xq, cuda), dev(wq, cuda), torch.tensor([sa], device=cuda), dev(ws, cuda), ready,
+                                               epoch, first, count, bias=dev(bias, cuda), relu=False)
+            torch.cuda.synchronize()
+            assert D.kernel_status(True) == 0, (which, M, N, K, first, count)
+            assert same(got.cpu().numpy(), port.linear_dequant(xq, wq, sa, ws, bias, relu=False)), (which, M, N, K, first, count)
+    finally:
+        D.gemm_backend(prev)
+
+
+def test_host_pipeline_seeded_random_shapes(cuda, lib, port):
+    """The host-buffer entry point with random row counts and row-block counts (1 to 16), calls in flight reusing
+    the two slots, on a layer created once for the largest."""
+    from rpl_b200 import device as D
+    from rpl_b200.sharded import RowShardedLinear
+    rng = np.random.default_rng(1618)
+    N, K, max_rows = 520, 256, 3000
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    wq, ws, _ = D.quantize_per_channel(dev(W, cuda))
+    hwq, hws, _ = port.quantize_per_channel(W, N)
+    layer = RowShardedLinear(wq, ws, dev(bias, cuda), n_total=N, max_rows=max_rows, rank=0, world=1)
+    pending = []
+    for _ in range(8):
+        M = int(rng.integers(1, max_rows + 1))
+        x = (rng.standard_normal((M, K)) * float(rng.choice([0.1, 1.0, 9.0]))).astype(np.float32)
+        xh = torch.from_numpy(x).pin_memory()
+        o = torch.full((M, N), -7.0, dtype=torch.float32).pin_memory()
+        layer.submit_host(xh, M, o, relu=True, row_blocks=int(rng.integers(1, 17)))
+        pending.append((x, xh, o))
+    layer.drain()
+    for x, _, o in pending:
+        hq, hs = port.quantize_symmetric(x)
+        assert same(o.numpy(), port.linear_dequant(hq, hwq, hs, hws, bias, relu=True)), x.shape
+    layer.close()
+    assert D.kernel_status(True) == 0
+
+
 # ---------------------------------------------------------------------------- two or more GPUs
 def _free_port():
     with socket.socket() as s:
