@@ -216,3 +216,77 @@ def test_quantize_fused_into_the_layer_any_shape(cuda, lib, port):
         assert (host(wide[:, :pad]) == GUARD_F32).all() and (host(wide[:, pad + N:]) == GUARD_F32).all(), ("guards", M, N, K, pad)
     torch.cuda.synchronize()
     assert D.kernel_status(True) == 0
+
+
+def test_reference_named_api_with_host_buffers_any_shape(cuda, lib, port):
+    """The calls a program written against the reference makes (host pointers in, library-owned host results out),
+    over random shapes: quantize in its three forms, per channel, dequantize, gemm_int8 with zero points and
+    linear_int8 with and without bias."""
+    import ctypes as C
+
+    from rpl_b200 import capi
+
+    def host_tensor(x):
+        shape = (C.c_uint32 * x.ndim)(*x.shape)
+        t = lib.tensor_create(x.ndim, shape, False)
+        C.memmove(t.contents.data, np.ascontiguousarray(x).ctypes.data, x.nbytes)
+        return t
+
+    def read(ptr, shape, dtype):
+        n = int(np.prod(shape))
+        buf = (C.c_char * (n * np.dtype(dtype).itemsize)).from_address(ptr)
+        return np.frombuffer(buf, dtype=dtype, count=n).reshape(shape).copy()
+
+    def qt_view(q):
+        t = capi.QuantizedTensor()
+        t.data = q.ctypes.data
+        t.scale, t.zero_point, t.size, t.dims = 1.0, 0, int(q.size), q.ndim
+        for i, s in enumerate(q.shape):
+            t.shape[i] = s
+        return t
+
+    rng = np.random.default_rng(8086)
+    for _ in range(10):
+        rows, cols = int(rng.integers(1, 400)), int(rng.integers(1, 3000))
+        x = (rng.standard_normal((rows, cols)) * float(rng.choice([0.01, 1.0, 50.0]))).astype(np.float32)
+        t = host_tensor(x)
+        scale, zp = float(rng.choice([0.02, 0.7])), int(rng.integers(-30, 30))
+        qt = lib.tensor_quantize_int8(t, scale, zp)
+        assert same(read(qt.contents.data, x.shape, np.int8), port.quantize(x, scale, zp)), ("explicit", rows, cols)
+        back = lib.tensor_dequantize_int8(qt)
+        assert same(read(back.contents.data, x.shape, np.float32), port.dequantize(port.quantize(x, scale, zp), scale, zp))
+        lib.tensor_free(back)
+        lib.quantized_tensor_free(qt)
+        qs = lib.tensor_quantize_int8_symmetric(t)
+        wq, ws = port.quantize_symmetric(x)
+        assert same(np.float32(qs.contents.scale), ws) and same(read(qs.contents.data, x.shape, np.int8), wq), ("symmetric", rows, cols)
+        lib.quantized_tensor_free(qs)
+        qa = lib.tensor_quantize_int8_asymmetric(t)
+        wq, ws, wz = port.quantize_asymmetric(x)
+        assert same(np.float32(qa.contents.scale), ws) and qa.contents.zero_point == wz, ("asymmetric", rows, cols)
+        assert same(read(qa.contents.data, x.shape, np.int8), wq), ("asymmetric", rows, cols)
+        lib.quantized_tensor_free(qa)
+        pc = lib.tensor_quantize_per_channel(t, 0)
+        wq, wsc, _ = port.quantize_per_channel(x, rows)
+        assert same(read(pc.contents.data, x.shape, np.int8), wq) and same(read(pc.contents.scales, (rows,), np.float32), wsc), \
+            ("per channel", rows, cols)
+        lib.per_channel_quantized_tensor_free(pc)
+        lib.tensor_free(t)
+    for i in range(10):
+        M, N, K = int(rng.integers(1, 400)), int(rng.integers(1, 400)), int(rng.integers(1, 900))
+        if i % 2:
+            N, K = 16 * max(1, N // 16), 16 * max(1, K // 16)          # the shapes the tensor cores take in place
+        A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+        B = np.ascontiguousarray(W.T)
+        b = rng.integers(-128, 128, N, dtype=np.int8)
+        out = np.full((M, N), GUARD_I32, np.int32)
+        za, zb = (int(rng.integers(-9, 9)), int(rng.integers(-9, 9))) if i % 3 else (0, 0)
+        lib.gemm_int8(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, N, K, 0.013, 0.021, 0.37, za, zb)
+        assert same(out, port.gemm_requant(A, B, 0.013, 0.021, 0.37, za, zb)), ("gemm_int8", M, N, K, za, zb)
+        qa, qw, qb = qt_view(A), qt_view(W), qt_view(b)
+        lib.linear_int8(C.byref(qa), C.byref(qw), None, out.ctypes.data, M, K, N)
+        assert same(out, port.linear(A, W)), ("linear_int8", M, N, K)
+        lib.linear_int8(C.byref(qa), C.byref(qw), C.byref(qb), out.ctypes.data, M, K, N)
+        assert same(out, port.linear(A, W, b)), ("linear_int8 + bias", M, N, K)
+    assert lib.rpl_cuda_last_error() == 0
