@@ -250,7 +250,8 @@ def _rank_main(rank, world, port_no, result_dir):
                                  rank=rank, world=world, column_counts=counts)
         assert (layer.col_begin, layer.col_count) == (b, c)
         # route 1: the rows travel by stores from a kernel; kernel 5: 256-row tiles, two arrival words per tile
-        for M, route, kernel in ((900, 0, 0), (1100, 1, 5), (640, 1, 0), (900, 0, 5)):
+        drawn = [(int(rng.integers(1, max_rows + 1)), int(rng.integers(0, 2)), int(rng.choice([0, 3, 5]))) for _ in range(6)]
+        for M, route, kernel in [(900, 0, 0), (1100, 1, 5), (640, 1, 0), (900, 0, 5)] + drawn:   # then six drawn from the shared seed
             layer.transfer(route)
             D.gemm_backend(kernel)
             x = rng.standard_normal((M, K)).astype(np.float32)
