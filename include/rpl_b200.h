@@ -139,10 +139,12 @@ int  rplb_free(void* dptr);
 typedef int (*rplb_alloc_fn)(void** dptr, size_t bytes);
 typedef int (*rplb_free_fn)(void* dptr);
 int  rplb_set_allocator(rplb_alloc_fn alloc_fn, rplb_free_fn free_fn);
-/* Scratch memory of the library: one block per (device, stream), allocated on
- * first use and grown (after a stream synchronize, by free + allocate) when a
- * call needs more: min/max partial results, a transposed B, row and column
- * sums.  A CUDA graph captured from rplb_* calls keeps the block's address, so
+/* Scratch memory of the library: one block per (device, stream, calling host
+ * thread), allocated on first use and grown (after a stream synchronize, by
+ * free + allocate) when a call needs more: min/max partial results, a
+ * transposed B, row and column sums.  Host threads never share a block, so
+ * they may call into the library at the same time, on the same stream or on
+ * different ones; reserve and release act on the calling thread's block.  A CUDA graph captured from rplb_* calls keeps the block's address, so
  * reserve the largest size the stream will ever need before capturing; a call
  * that would have to grow the block of a capturing stream fails with
  * RPLB_E_UNSUPPORTED instead.  release frees the block of a stream that is

@@ -17,11 +17,12 @@ int cuda_ok(cudaError_t e, const char* what);
 // Checks the launch that was just issued and counts it.
 int launched(const char* kernel);
 
-// Scratch memory owned by the library, one block per (device, stream),
-// allocated with cudaMalloc on first use and grown when a call needs more.
-// Contents: [0, 64) control words kept zero between calls (ticket counters),
-// then `bytes` of uninitialised space.  Calls on the same stream are ordered
-// by the stream, so they can share it.
+// Scratch memory owned by the library, one block per (device, stream, host
+// thread), allocated with cudaMalloc on first use and grown when a call needs
+// more.  Contents: [0, 64) control words kept zero between calls (ticket
+// counters), then `bytes` of uninitialised space.  One thread's calls on one
+// stream are ordered by the stream, so they can share it; another thread's
+// kernels may be queued between two kernels of a call, so it gets its own.
 struct Scratch {
     unsigned int* control;   // 16 words, zero at kernel entry, kernels restore zero
     void* data;              // at least the requested size, 256-byte aligned

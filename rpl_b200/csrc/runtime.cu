@@ -7,6 +7,8 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <thread>
+#include <tuple>
 #include <utility>
 
 namespace rplb {
@@ -39,8 +41,13 @@ struct ScratchBlock {
     void* base = nullptr;
     size_t bytes = 0;
 };
+// One block per (device, stream, host thread): two host threads that use the same stream (the reference-named API
+// runs every thread on the default stream) must not share a block, because a call keeps data in it between two of
+// its own kernels (a transposed B, row and column sums, min/max partials) and the other thread's kernels can be
+// queued in between.
+typedef std::tuple<int, cudaStream_t, std::thread::id> ScratchKey;
 static std::mutex g_scratch_mu;
-static std::map<std::pair<int, cudaStream_t>, ScratchBlock> g_scratch;
+static std::map<ScratchKey, ScratchBlock> g_scratch;
 static constexpr size_t kControlBytes = 256;
 
 // Device allocator behind rplb_malloc / rplb_free and the scratch blocks:
@@ -71,7 +78,7 @@ int scratch_for(cudaStream_t stream, size_t bytes, Scratch* out) {
     int dev = 0;
     if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
     std::lock_guard<std::mutex> lock(g_scratch_mu);
-    ScratchBlock& b = g_scratch[std::make_pair(dev, stream)];
+    ScratchBlock& b = g_scratch[ScratchKey(dev, stream, std::this_thread::get_id())];
     size_t want = kControlBytes + ((bytes + 255) & ~size_t(255));
     if (b.bytes < want) {
         // A block cannot be allocated, grown or cleared while the stream records a
@@ -163,7 +170,7 @@ int rplb_scratch_release(void* stream) {
     if (int rc = cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
     cudaStream_t st = as_stream(stream);
     std::lock_guard<std::mutex> lock(g_scratch_mu);
-    auto it = g_scratch.find(std::make_pair(dev, st));
+    auto it = g_scratch.find(ScratchKey(dev, st, std::this_thread::get_id()));
     if (it == g_scratch.end()) return 0;
     if (it->second.base) {
         if (int rc = cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return rc;

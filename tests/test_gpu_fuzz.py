@@ -290,3 +290,51 @@ def test_reference_named_api_with_host_buffers_any_shape(cuda, lib, port):
         lib.linear_int8(C.byref(qa), C.byref(qw), C.byref(qb), out.ctypes.data, M, K, N)
         assert same(out, port.linear(A, W, b)), ("linear_int8 + bias", M, N, K)
     assert lib.rpl_cuda_last_error() == 0
+
+
+def test_reference_named_api_from_several_host_threads(cuda, lib, port):
+    """The reference's functions are stateless and re-entrant; so are these.  Four host threads call gemm_int8
+    (shapes that need the library's scratch memory: a transposed copy of B, row and column sums for the zero
+    points), linear_int8 and the symmetric quantize at the same time, each on its own data."""
+    import ctypes as C
+    import threading
+
+    from rpl_b200 import capi
+
+    def work(seed, failures):
+        try:
+            rng = np.random.default_rng(seed)
+            for i in range(12):
+                M, N, K = int(rng.integers(100, 400)), int(rng.integers(17, 300)), 16 * int(rng.integers(4, 40))
+                if i % 2:
+                    N |= 1                                      # B[K,N] cannot be read in place: transposed copy in scratch
+                A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+                B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+                out = np.zeros((M, N), np.int32)
+                za, zb = int(rng.integers(-9, 9)), int(rng.integers(-9, 9))
+                lib.gemm_int8(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, N, K, 0.013, 0.021, 0.37, za, zb)
+                if not same(out, port.gemm_requant(A, B, 0.013, 0.021, 0.37, za, zb)):
+                    failures.append(("gemm_int8", seed, i, M, N, K, za, zb))
+                x = (rng.standard_normal((int(rng.integers(1, 200)), int(rng.integers(1, 5000)))) * 3).astype(np.float32)
+                shape = (C.c_uint32 * 2)(*x.shape)
+                t = lib.tensor_create(2, shape, False)
+                C.memmove(t.contents.data, x.ctypes.data, x.nbytes)
+                qs = lib.tensor_quantize_int8_symmetric(t)
+                wq, ws = port.quantize_symmetric(x)
+                n = x.size
+                got = np.frombuffer((C.c_char * n).from_address(qs.contents.data), dtype=np.int8, count=n).reshape(x.shape)
+                if not (same(np.float32(qs.contents.scale), ws) and same(got, wq)):
+                    failures.append(("quantize_symmetric", seed, i, x.shape))
+                lib.quantized_tensor_free(qs)
+                lib.tensor_free(t)
+        except Exception as e:                                  # a failure inside a thread must reach the test
+            failures.append(("exception", seed, repr(e)))
+
+    failures = []
+    threads = [threading.Thread(target=work, args=(1000 + k, failures)) for k in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not failures, failures[:5]
+    assert lib.rpl_cuda_last_error() == 0
