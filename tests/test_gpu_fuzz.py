@@ -338,3 +338,46 @@ def test_reference_named_api_from_several_host_threads(cuda, lib, port):
         th.join()
     assert not failures, failures[:5]
     assert lib.rpl_cuda_last_error() == 0
+
+
+def test_two_devices_in_one_process_from_two_threads(lib, port):
+    """One host thread per GPU in the same process (the library's caches are keyed by device, its switches and
+    status words by thread): quantize and GEMM on both devices at once, each against the checker."""
+    import threading
+
+    from rpl_b200 import device as D
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+
+    def work(ordinal, failures):
+        try:
+            torch.cuda.set_device(ordinal)
+            d = torch.device("cuda", ordinal)
+            rng = np.random.default_rng(50 + ordinal)
+            for i in range(8):
+                M, N, K = int(rng.integers(100, 900)), int(rng.integers(17, 600)), 16 * int(rng.integers(4, 40))
+                x = (rng.standard_normal((M, K)) * 2).astype(np.float32)
+                W = rng.integers(-128, 128, (N, K), dtype=np.int8)
+                ws = ((rng.random(N) + 0.5) * 1e-3).astype(np.float32)
+                D.gemm_backend([0, 3, 4, 5][i % 4])
+                xq, params = D.quantize_symmetric(torch.from_numpy(x).to(d))
+                got = D.linear_i8_dequant(xq, torch.from_numpy(W).to(d), params[D.QPARAM_SCALE_SYM:D.QPARAM_SCALE_SYM + 1],
+                                          torch.from_numpy(ws).to(d))
+                torch.cuda.synchronize(d)
+                hq, hs = port.quantize_symmetric(x)
+                if not (same(host(xq), hq) and same(host(got), port.linear_dequant(hq, W, hs, ws))):
+                    failures.append((ordinal, i, M, N, K))
+            D.gemm_backend(0)
+            if D.kernel_status(True) != 0:
+                failures.append((ordinal, "status"))
+        except Exception as e:
+            failures.append((ordinal, repr(e)))
+
+    failures = []
+    threads = [threading.Thread(target=work, args=(k, failures)) for k in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    torch.cuda.set_device(0)
+    assert not failures, failures[:5]

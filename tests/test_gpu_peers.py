@@ -23,12 +23,17 @@ def same(a, b):
     return np.array_equal(bits(np.asarray(a)), bits(np.asarray(b)))
 
 
-@pytest.mark.parametrize("mnk,relu", [((300, 512, 256), False), ((129, 250, 64), True), ((128, 256, 128), False)])
-def test_extra_destinations_on_one_device(cuda, lib, port, mnk, relu):
+@pytest.mark.parametrize("mnk,relu,round_up", [((300, 512, 256), False, False), ((129, 250, 64), True, False), ((128, 256, 128), False, False),
+                                              ((129, 250, 64), True, True), ((200, 301, 128), False, True)])
+def test_extra_destinations_on_one_device(cuda, lib, port, mnk, relu, round_up):
     from rpl_b200 import capi, device as D
     from rpl_b200.sharded import _RawBlock
     M, N, K = mnk
     n_total, begin = N + 256 + 8, 256                 # this "rank" owns columns [256, 256 + N) of a wider matrix
+    if round_up:
+        # a row stride of whole 16-byte pieces under a block whose width is not: tensor stores for the whole
+        # chunks, the ragged last chunk from registers, the staged copy for the peers either way
+        n_total = (n_total + 3) // 4 * 4
     rng = np.random.default_rng(61)
     xq = rng.integers(-128, 128, (M, K), dtype=np.int8)
     wq = rng.integers(-128, 128, (N, K), dtype=np.int8)
