@@ -269,6 +269,41 @@ def _rank_main(rank, world, port_no, result_dir):
         D.gemm_backend(0)
         dist.barrier()
         layer.close()
+        # two layers in a chain, each with its own communicator: column blocks of the first are gathered, every
+        # rank takes its rows of the result as its share of the second layer's input (with four ranks the last one
+        # owns no column of the second layer and still quantizes and sends its rows)
+        n2 = 768
+        W2 = (rng.standard_normal((n2, n_total)) * 0.05).astype(np.float32)
+        hw2q, hw2s, _ = cpu.quantize_per_channel(W2, n2)
+        b1, c1 = RowShardedLinearColumns(n_total, world, rank)
+        w1q, w1s, _ = D.quantize_per_channel(torch.from_numpy(W[b1:b1 + c1]).to(dev_))
+        first = RowShardedLinear(w1q, w1s, torch.from_numpy(bias[b1:b1 + c1]).to(dev_), n_total=n_total, max_rows=max_rows,
+                                 rank=rank, world=world)
+        b2, c2 = RowShardedLinearColumns(n2, world, rank)
+        if c2:
+            w2q, w2s, _ = D.quantize_per_channel(torch.from_numpy(W2[b2:b2 + c2]).to(dev_))
+        else:
+            w2q, w2s = torch.empty((0, n_total), dtype=torch.int8, device=dev_), torch.empty(0, device=dev_)
+        second = RowShardedLinear(w2q, w2s, None, n_total=n2, max_rows=max_rows, rank=rank, world=world)
+        for M in (1000, 333):
+            x = rng.standard_normal((M, K)).astype(np.float32)
+            r0, rc = first.rows(M)
+            h_block = first.forward(torch.from_numpy(np.ascontiguousarray(x[r0:r0 + rc])).to(dev_), M, relu=True)
+            h_full = first.gather(h_block, M)
+            r0b, rcb = second.rows(M)
+            y_block = second.forward(h_full[r0b:r0b + rcb].contiguous(), M)
+            y_full = second.gather(y_block, M)
+            torch.cuda.synchronize()
+            hq, hs = cpu.quantize_symmetric(x)
+            want_h = cpu.linear_dequant(hq, hwq, hs, hws, bias, relu=True)
+            h2q, h2s = cpu.quantize_symmetric(want_h)
+            want_y = cpu.linear_dequant(h2q, hw2q, h2s, hw2s, None, relu=False)
+            assert np.array_equal(h_full.cpu().numpy().view(np.uint32), want_h.view(np.uint32)), "chain, first layer, rank %d" % rank
+            assert np.array_equal(y_full.cpu().numpy().view(np.uint32), want_y.view(np.uint32)), "chain, second layer, rank %d" % rank
+            assert D.kernel_status(True) == 0
+        dist.barrier()
+        second.close()
+        first.close()
         with open(os.path.join(result_dir, "ok%d" % rank), "w") as f:
             f.write("ok")
     finally:
