@@ -413,9 +413,10 @@ int  rplb_selftest_bounded_wait_keep(void* stream);
  * 256x256 tile (two accumulators), 6 = the tcgen05 kernel for few output
  * features (N <= 128, K <= 896, fp32 epilogue only; the automatic choice for
  * such layers over many rows); 0 and 2 pick between 3, 4, 5 and 6 by shape:
- * 5 for GEMMs of 1.1e12 multiply-accumulates and more (measured: the most work
- * per joule, and a long GEMM runs at the board's power limit), 4 for shorter
- * ones that give every SM pair a tile, 3 otherwise.  The sharded layer with
+ * 5 for GEMMs of 1.1e12 multiply-accumulates and more with K >= 6144 (measured:
+ * the most work per joule, and a long GEMM runs at the board's power limit;
+ * its epilogue is not overlapped, so a short reduction does not pay), 4 for
+ * GEMMs under 1.1e12 that give every SM pair a tile, 3 otherwise.  The sharded layer with
  * several ranks honours 3 and 5 (the kernels that can wait for arriving rows)
  * and chooses between them itself for any other value.
  * Returns the previous setting.  All of them are CUDA kernels. */

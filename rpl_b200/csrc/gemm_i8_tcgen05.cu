@@ -963,13 +963,17 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     }
     // A GEMM long enough for the board to settle on its power cap: what counts then is work per joule.
     const bool sustained = (double)p.M * (double)p.N * (double)p.K >= 1.1e12;
+    // The 256 x 256 kernel does not overlap a tile's epilogue with the next tile's main loop, so it needs a long
+    // reduction to come out ahead: +4 % at K = 8192, -1.5 % at K = 4096 (the fused Q/K/V projection) against
+    // the 128 x 256 kernel.
+    const bool wide_pays = sustained && p.K >= 6144;
     if (p.a_ready) {
         // The 128 x 256 kernel and the 256 x 256 kernel wait for rows that are still arriving.
         const uint64_t tiles_m = (p.M + TILE_M - 1) / TILE_M;
         if (p.b_is_kn || (uint64_t)p.a_local_first + p.a_local_count > tiles_m || (p.a_local_first >= tiles_m && tiles_m))
             return fail(RPLB_E_BAD_ARG, "arriving rows: local blocks [%u, +%u) outside the %llu row blocks of A",
                         p.a_local_first, p.a_local_count, (unsigned long long)tiles_m);
-        variant = (variant == 3 || (variant == 0 && sustained)) ? 3 : 1;
+        variant = (variant == 3 || (variant == 0 && wide_pays)) ? 3 : 1;
     }
     if (variant == 4) return gemm_narrow(p, st);         // asked for by name: refused if the shape does not fit
     if (variant == 0 && gemm_narrow_supports(p) && p.M >= (uint64_t)TILE_M * sms) {
@@ -986,10 +990,12 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
         // operand traffic into the SM) runs at ~1.42 GHz against ~1.38 GHz and is
         // ~4 % faster than the 128 x 256 kernel, which in turn beats the pair kernel
         // by ~6 %.  So: the 256 x 256 kernel for GEMMs long enough for the governor
-        // to settle; the pair kernel for shorter ones, provided every pair of SMs
-        // gets a 256 x 256 tile of its own; the 128 x 256 kernel otherwise.
+        // to settle whose reduction is long enough to hide its exposed epilogue; the
+        // 128 x 256 kernel for the other long ones; the pair kernel for shorter ones,
+        // provided every pair of SMs gets a 256 x 256 tile of its own; the 128 x 256
+        // kernel otherwise.
         const uint64_t pair_tiles = ((p.M + PAIR_TILE_M - 1) / PAIR_TILE_M) * ((p.N + TILE_N - 1) / TILE_N);
-        variant = sustained ? 3 : (pair_tiles >= sms / 2 ? 2 : 1);
+        variant = wide_pays ? 3 : (sustained ? 1 : (pair_tiles >= sms / 2 ? 2 : 1));
     }
     CUtensorMap ma, mw, mo;
     int tma_out = 0;
