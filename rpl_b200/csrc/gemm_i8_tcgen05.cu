@@ -460,7 +460,7 @@ struct __align__(16) WideShared {
     uint64_t full[kWideStages];
     uint64_t empty[kWideStages];
     uint64_t acc_full;               // MMA -> epilogue: both accumulators complete
-    uint64_t acc_empty;              // epilogue -> MMA: both accumulators drained
+    uint64_t acc_empty[2];           // epilogue -> MMA: the upper / the lower accumulator drained
     uint32_t tmem_base;
     volatile int abort_flag;
     float w_scales[4 * TILE_N];
@@ -485,7 +485,8 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWideStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
         mbar_init(&sh->acc_full, 1);
-        mbar_init(&sh->acc_empty, kEpilogueThreads / 32);
+        mbar_init(&sh->acc_empty[0], kEpilogueThreads / 32);
+        mbar_init(&sh->acc_empty[1], kEpilogueThreads / 32);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -532,23 +533,54 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t stage = 0, phase = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                if (!mbar_wait_bounded(&sh->acc_empty, acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) break;
+                // The epilogue drains the upper accumulator first.  As soon as that one is free the next tile's
+                // main loop starts on it; the MMAs of the lower half of up to kWideStages K blocks are held back
+                // (their stages stay occupied) until the lower accumulator is free too, so about half of the
+                // epilogue runs under tensor work although both accumulators belong to one tile.
+                if (!mbar_wait_bounded(&sh->acc_empty[0], acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) break;
                 tc_fence_after();
+                bool lower_free = false;
+                uint32_t held = 0, held_stage[kWideStages], held_kb[kWideStages];
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait_bounded(&sh->full[stage], phase, &sh->abort_flag, status, TC_WAIT_FULL)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + (size_t)stage * WIDE_STAGE_BYTES);
-                    const uint64_t a_lo = make_kmajor_sw128_desc(a_addr);
-                    const uint64_t a_hi = make_kmajor_sw128_desc(a_addr + 128 * TILE_K);     // rows 128..255 of the A stage
-                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + WIDE_A_BYTES);
-                    #pragma unroll
-                    for (int k = 0; k < TILE_K / MMA_K; k++) {
-                        const uint64_t adv = (uint64_t)(k * (MMA_K >> 4));
-                        const uint32_t accumulate = (kb | (uint32_t)k) != 0 ? 1u : 0u;
-                        tc_mma_i8(tmem_base, a_lo + adv, b_desc + adv, kIdescI8, accumulate);             // columns 0..255
-                        tc_mma_i8(tmem_base + TILE_N, a_hi + adv, b_desc + adv, kIdescI8, accumulate);    // columns 256..511
+                    {
+                        const uint32_t a_addr = smem_u32(smem + (size_t)stage * WIDE_STAGE_BYTES);
+                        const uint64_t a_lo = make_kmajor_sw128_desc(a_addr);
+                        const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + WIDE_A_BYTES);
+                        #pragma unroll
+                        for (int k = 0; k < TILE_K / MMA_K; k++) {
+                            const uint64_t adv = (uint64_t)(k * (MMA_K >> 4));
+                            tc_mma_i8(tmem_base, a_lo + adv, b_desc + adv, kIdescI8, (kb | (uint32_t)k) != 0 ? 1u : 0u);   // columns 0..255
+                        }
                     }
-                    tc_commit(&sh->empty[stage]);
+                    held_stage[held] = stage;
+                    held_kb[held] = kb;
+                    held++;
+                    if (!lower_free) {
+                        if (held == (uint32_t)kWideStages || kb + 1 == num_kb) {
+                            // Every stage is held (or the tile ends): nothing more can be done without the lower accumulator.
+                            if (!mbar_wait_bounded(&sh->acc_empty[1], acc_phase ^ 1, &sh->abort_flag, status, TC_WAIT_ACC_EMPTY)) { ok = false; break; }
+                            lower_free = true;
+                        } else {
+                            lower_free = mbar_try_wait(&sh->acc_empty[1], acc_phase ^ 1);
+                        }
+                        if (lower_free) tc_fence_after();
+                    }
+                    if (lower_free) {
+                        for (uint32_t h = 0; h < held; h++) {
+                            const uint32_t a_addr = smem_u32(smem + (size_t)held_stage[h] * WIDE_STAGE_BYTES);
+                            const uint64_t a_hi = make_kmajor_sw128_desc(a_addr + 128 * TILE_K);     // rows 128..255 of the A stage
+                            const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + WIDE_A_BYTES);
+                            #pragma unroll
+                            for (int k = 0; k < TILE_K / MMA_K; k++) {
+                                const uint64_t adv = (uint64_t)(k * (MMA_K >> 4));
+                                tc_mma_i8(tmem_base + TILE_N, a_hi + adv, b_desc + adv, kIdescI8, (held_kb[h] | (uint32_t)k) != 0 ? 1u : 0u);   // columns 256..511
+                            }
+                            tc_commit(&sh->empty[held_stage[h]]);
+                        }
+                        held = 0;
+                    }
                     if (++stage == kWideStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
@@ -594,10 +626,11 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     epilogue_chunk<MODE, false>(p, &map_out, tma, my_tile, r, m_base, lane, n_first, a_scale,
                                                 s_scales + chunk * 32, s_bias + chunk * 32, oq, row_sum, absmax);
                 }
+                // This half's accumulator has been read: the next tile's MMAs may overwrite it.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->acc_empty[half]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->acc_empty);
             acc_phase ^= 1;
         }
         if (tma && lane == 0) bulk_wait_all();
