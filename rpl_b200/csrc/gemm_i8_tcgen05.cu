@@ -450,6 +450,10 @@ gemm_i8_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // cap what counts is energy per operation, not idle cycles.
 constexpr int WIDE_TILE_M = 256;
 constexpr int kWideStages = 3;
+constexpr int kWideEpilogueWarps = 8;                     // two per TMEM lane quarter, each takes every other 32-column chunk
+constexpr int WIDE_THREADS = (2 + kWideEpilogueWarps) * 32;
+constexpr uint32_t WIDE_EPI_BYTES = kWideEpilogueWarps * EPI_TILE_BYTES;   // a 4 KiB staging tile per epilogue warp
+constexpr uint32_t kWideEpilogueBarrier = 1;              // named barrier of the eight epilogue warps (0 is __syncthreads')
 constexpr uint32_t WIDE_A_BYTES = WIDE_TILE_M * TILE_K;   // 32 KiB
 constexpr uint32_t WIDE_B_BYTES = TILE_N * TILE_K;        // 32 KiB
 constexpr uint32_t WIDE_STAGE_BYTES = WIDE_A_BYTES + WIDE_B_BYTES;
@@ -463,30 +467,40 @@ struct __align__(16) WideShared {
     uint64_t acc_empty[2];           // epilogue -> MMA: the upper / the lower accumulator drained
     uint32_t tmem_base;
     volatile int abort_flag;
-    float w_scales[4 * TILE_N];
-    float bias[4 * TILE_N];
+    alignas(16) float w_scales[TILE_N];   // one copy for all epilogue warps (the eight staging tiles leave no room for more)
+    alignas(16) float bias[TILE_N];
 };
-constexpr size_t WIDE_SMEM_BYTES = 1024 + (size_t)kWideStages * WIDE_STAGE_BYTES + EPI_STAGE_BYTES + sizeof(WideShared);
+// The stage ring needs a 1024-byte aligned base.  Dynamic shared memory starts at a 128-byte boundary at least on
+// this architecture (in practice at a 1024-byte one), so 896 bytes of slack are asked for instead of 1024: with the
+// eight staging tiles every byte counts (232,400 of the 232,448 a CTA may have).  The kernel checks the assumption
+// and gives up with a status code, touching nothing, if it ever fails.
+constexpr size_t WIDE_ALIGN_SLACK = 896;
+constexpr size_t WIDE_SMEM_BYTES = WIDE_ALIGN_SLACK + (size_t)kWideStages * WIDE_STAGE_BYTES + WIDE_EPI_BYTES + sizeof(WideShared);
+static_assert(WIDE_SMEM_BYTES <= 232448, "the 256 x 256 kernel's shared memory exceeds what a CTA may have");
 
 template <int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(WIDE_THREADS, 1)
 gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_out, const GemmProblem p, uint32_t tiles_m, uint32_t tiles_n,
                        uint32_t num_kb, int tma_out, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* epi_tiles = smem + (size_t)kWideStages * WIDE_STAGE_BYTES;
-    WideShared* sh = reinterpret_cast<WideShared*>(epi_tiles + EPI_STAGE_BYTES);
+    WideShared* sh = reinterpret_cast<WideShared*>(epi_tiles + WIDE_EPI_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
+    if ((size_t)(smem - smem_raw) > WIDE_ALIGN_SLACK) {   // never seen; see WIDE_ALIGN_SLACK
+        if (threadIdx.x == 0) atomicCAS(status, 0, (int)TC_WAIT_EMPTY);
+        return;
+    }
     // Walk the m-tiles starting at the tile that holds the first block of A in place at launch.
     const uint32_t rotate = p.a_ready ? p.a_local_first / 2 : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWideStages; s++) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
         mbar_init(&sh->acc_full, 1);
-        mbar_init(&sh->acc_empty[0], kEpilogueThreads / 32);
-        mbar_init(&sh->acc_empty[1], kEpilogueThreads / 32);
+        mbar_init(&sh->acc_empty[0], kWideEpilogueWarps);
+        mbar_init(&sh->acc_empty[1], kWideEpilogueWarps);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -591,10 +605,16 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         __syncwarp();
     } else {
         // ------------------------------------------------------------- epilogue
+        // Eight warps.  The epilogue of this kernel is not hidden under a main loop (both accumulators belong to one
+        // tile), and measured with timestamps it is a chain of latencies per 32-column chunk (TMEM load, conversion,
+        // staging, proxy fence, store issue: about 800 cycles) that a warp walks once per chunk it owns.  The two
+        // warps that may read a TMEM lane quarter therefore take every other chunk each, with a staging tile of
+        // their own: eight steps per tile and warp instead of sixteen.
         const uint32_t quarter = (uint32_t)warp & 3u;
         const int ew = warp - kEpilogueWarp0;
-        float* s_scales = sh->w_scales + ew * TILE_N;
-        float* s_bias = sh->bias + ew * TILE_N;
+        const int first_chunk = ew >> 2;                     // warps 2-5: chunks 0, 2, 4, 6; warps 6-9: chunks 1, 3, 5, 7
+        float* s_scales = sh->w_scales;
+        float* s_bias = sh->bias;
         uint8_t* my_tile = epi_tiles + ew * EPI_TILE_BYTES;
         const bool tma = tma_out != 0;
         const float a_scale = (MODE == EPI_DEQUANT_F32 || MODE == EPI_DEQUANT_I8) ? __ldg(p.a_scale) : 0.0f;
@@ -606,10 +626,16 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn, WIDE_GROUP_M, rotate);
             const uint64_t n0 = (uint64_t)tn * TILE_N;
-            if (n0 != staged_n0) { stage_columns<MODE>(p, n0, lane, s_scales, s_bias); staged_n0 = n0; }
             bool ok = mbar_wait_bounded(&sh->acc_full, acc_phase, &sh->abort_flag, status, TC_WAIT_ACC_FULL);
-            ok = __all_sync(0xffffffffu, ok);
+            // All eight warps go on, or none: they are about to meet at a barrier.  Everyone who arrives here has
+            // also finished the previous tile, so the shared per-column values may be replaced.
+            ok = named_barrier_all(kWideEpilogueBarrier, kWideEpilogueWarps * 32, ok);
             if (!ok) break;
+            if (n0 != staged_n0) {                           // the same test in every warp
+                if (ew == 0) stage_columns<MODE>(p, n0, lane, s_scales, s_bias);
+                named_barrier(kWideEpilogueBarrier, kWideEpilogueWarps * 32);
+                staged_n0 = n0;
+            }
             tc_fence_after();
             #pragma unroll 1
             for (int half = 0; half < 2; half++) {
@@ -617,7 +643,7 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint64_t m = m_base + lane;
                 const int32_t row_sum = (MODE == EPI_REQUANT_I32 && p.a_row_sums && m < p.M) ? __ldg(p.a_row_sums + m) : 0;
                 #pragma unroll 1
-                for (int chunk = 0; chunk < TILE_N / 32; chunk++) {
+                for (int chunk = first_chunk; chunk < TILE_N / 32; chunk += 2) {
                     const uint64_t n_first = n0 + (uint64_t)chunk * 32;
                     if (n_first >= p.N) break;
                     uint32_t r[32];
@@ -967,7 +993,7 @@ static int launch_tc_wide(const CUtensorMap& ma, const CUtensorMap& mw, const CU
     const uint32_t tiles_n = (uint32_t)((p.N + TILE_N - 1) / TILE_N);
     const uint64_t tiles = (uint64_t)tiles_m * tiles_n;
     const unsigned int grid = (unsigned int)(tiles < sms ? tiles : sms);
-    gemm_i8_tc_wide_kernel<MODE><<<grid, TC_THREADS, WIDE_SMEM_BYTES, st>>>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev);
+    gemm_i8_tc_wide_kernel<MODE><<<grid, WIDE_THREADS, WIDE_SMEM_BYTES, st>>>(ma, mw, mo, p, tiles_m, tiles_n, num_kb, tma_out, status_dev);
     return launched("gemm_i8_tc_wide_kernel");
 }
 

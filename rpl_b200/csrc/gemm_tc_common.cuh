@@ -172,6 +172,23 @@ __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, 
 constexpr uint32_t kIdescI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 constexpr uint32_t kIdescI8BMn = kIdescI8 | (1u << 16);      // B operand MN-major: gemm_int8's B[K,N] as it lies in memory
 
+// A named barrier over `threads` threads with a vote: true only if every participant passed true.  Used after a
+// bounded wait by warps that go on to meet at barriers, so that they all take the same decision (one that gave up
+// while another just got through would otherwise leave its partners waiting for ever).
+__device__ __forceinline__ bool named_barrier_all(uint32_t barrier_id, uint32_t threads, bool mine) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.and.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out) : "r"(barrier_id), "r"(threads), "r"(mine ? 1u : 0u) : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void named_barrier(uint32_t barrier_id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(threads) : "memory");
+}
+
 // Tile index -> (m-tile, n-tile): tiles are numbered so that CTAs running at the
 // same time cover GROUP_M consecutive m-tiles of a few n-tiles, which keeps the
 // set of A and W rows being streamed small enough to be served from L2.
