@@ -843,10 +843,10 @@ def run_ours(a):
         return
 
     # DRAM traffic of the GEMM from ncu captures at 16384 x 16384 x 8192 (dram read + write) per output element
-    # at K = 8192: 9.39 B for the kernel with 256 x 256 tiles (the library's choice for a GEMM this long),
+    # at K = 8192: 9.42 B for the kernel with 256 x 256 tiles (the library's choice for a GEMM this long),
     # 7.13 B for the kernel with 128 x 256 tiles.
     wide = a.gemm_backend == 5 or (a.gemm_backend == 0 and float(M) * count * K >= 1.1e12 and K >= 6144)
-    traffic = (9.39 if wide else 7.13) * M * count if K == 8192 and a.gemm_backend in (0, 3, 5) else None
+    traffic = (9.42 if wide else 7.13) * M * count if K == 8192 and a.gemm_backend in (0, 3, 5) else None
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = ops_rank / (gemm_ms * 1e-3) / 1e12
     sched = ("every rank: min/max of its rows, max-all-reduce of (-min, max), quantize its rows, peer copies of the int8 rows "
