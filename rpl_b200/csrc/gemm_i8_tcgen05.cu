@@ -1023,7 +1023,7 @@ int gemm_tcgen05(const GemmProblem& p, cudaStream_t st, int variant) {
     // A GEMM long enough for the board to settle on its power cap: what counts then is work per joule.
     const bool sustained = (double)p.M * (double)p.N * (double)p.K >= 1.1e12;
     // The 256 x 256 kernel does not overlap a tile's epilogue with the next tile's main loop, so it needs a long
-    // reduction to come out ahead: +4 % at K = 8192, -1.5 % at K = 4096 (the fused Q/K/V projection) against
+    // reduction to come out ahead: +4 % at K = 8192, -1 % at K = 4096 (the fused Q/K/V projection) against
     // the 128 x 256 kernel.
     const bool wide_pays = sustained && p.K >= 6144;
     if (p.a_ready) {
