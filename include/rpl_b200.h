@@ -389,7 +389,9 @@ int  rplb_relu_f32_inplace(float* x, uint64_t n, void* stream);
  * 0, or the code of the bounded wait that expired (1 stage-free, 2 stage-loaded,
  * 3 accumulator-free, 4 accumulator-ready, 5 rows from another GPU; 6 = a bulk
  * copy of the per-channel quantizer's staged rows did not complete, 7 = the
- * grid barrier of the one-launch per-tensor quantizer).  Every
+ * grid barrier of the one-launch per-tensor quantizer, 8 = the 256x256
+ * kernel found its shared memory starting off a 128-byte boundary and did
+ * nothing: never seen on sm_100a, checked because the kernel counts on it).  Every
  * host thread has a word of its own, so a give-up is seen by the thread that
  * launched the kernel (and refuses that thread's next GEMM until cleared).
  * Readable at any time; clear != 0 resets it.  A kernel that gave up leaves

@@ -490,7 +490,7 @@ gemm_i8_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t total_tiles = tiles_m * tiles_n;      // tiles of 256 x 256
     if ((size_t)(smem - smem_raw) > WIDE_ALIGN_SLACK) {   // never seen; see WIDE_ALIGN_SLACK
-        if (threadIdx.x == 0) atomicCAS(status, 0, (int)TC_WAIT_EMPTY);
+        if (threadIdx.x == 0) atomicCAS(status, 0, (int)TC_SMEM_BASE);
         return;
     }
     // Walk the m-tiles starting at the tile that holds the first block of A in place at launch.

@@ -17,7 +17,7 @@ constexpr uint32_t EPI_TILE_BYTES = 32 * 128;            // one epilogue warp's 
 constexpr uint32_t EPI_STAGE_BYTES = 4 * EPI_TILE_BYTES;  // four epilogue warps; follows the stage ring, so it is 1024-byte aligned
 
 // Status codes written to the status word when a wait gives up.
-enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4, TC_WAIT_ROWS = 5, TC_WAIT_SELFTEST = 99 };
+enum : int { TC_WAIT_EMPTY = 1, TC_WAIT_FULL = 2, TC_WAIT_ACC_EMPTY = 3, TC_WAIT_ACC_FULL = 4, TC_WAIT_ROWS = 5, TC_SMEM_BASE = 8, TC_WAIT_SELFTEST = 99 };
 
 // --------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
