@@ -58,8 +58,10 @@ def parse_args():
                          "replicated: every rank holds and quantizes all of A (comparison only, N > 1)")
     ap.add_argument("--no-numa", action="store_true", help="allocate the page-locked host buffers wherever the process happens to run "
                     "(default: on the CPUs next to the rank's GPU)")
-    ap.add_argument("--no-balance", action="store_true", help="N > 1: keep the even column split instead of re-splitting the columns "
-                    "in proportion to each GPU's GEMM speed measured during warm-up")
+    ap.add_argument("--balance", action="store_true", help="N > 1: re-split the columns in proportion to each GPU's GEMM speed measured "
+                    "under load before the timed region (off by default: measured, the ranking of the GPUs of a node under "
+                    "their power cap does not hold from one second to the next, and the re-split cost 0-3 %)")
+    ap.add_argument("--no-balance", action="store_true", help="accepted for older command lines: the even split is the default")
     ap.add_argument("--transfer", type=int, default=0, help="N > 1: how the int8 rows reach the other ranks: 0 copy engines (default), "
                     "1 stores from a second quantize kernel (comparison)")
     ap.add_argument("--balance-threshold", type=float, default=1.06,
@@ -608,7 +610,7 @@ def run_ours(a):
     # ---- N > 1: the GPUs of a node do not sustain the same clock under their power cap, and a step ends when the
     # slowest rank does.  Measure every rank's GEMM under sustained load and deal the columns out in proportion to speed. ----
     balance = None
-    if world > 1 and not replicated and not a.no_balance:
+    if world > 1 and not replicated and a.balance and not a.no_balance:
         from rpl_b200.sharded import weighted_column_counts
         # About a second of steps first: what counts is the clock each GPU settles at under its power cap, and a
         # cold GPU runs faster than that.  Every rank runs the same number of steps (a step contains a collective).
